@@ -127,7 +127,8 @@ class CacheManager:
         """Pages group ``group`` must hold for a request with ``committed`` tokens stored
         that is about to hold ``total``."""
         first = self._first_live_page(group, committed)
-        return max(0, -(-total // self.page_size) - first)
+        last = -(-total // self.page_size)
+        return max(0, last - first) + min(self._kept_pages(group), first, last)
 
     def _first_live_page(self, group: int, committed: int) -> int:
         need = self.needs[group]
@@ -139,6 +140,14 @@ class CacheManager:
         if need.chunk:
             oldest = max(oldest, committed - committed % need.chunk)
         return oldest // self.page_size
+
+    def _kept_pages(self, group: int) -> int:
+        """Pages at the head of a request's table that a windowed group never gives back:
+        those that hold any of the first ``keep_first`` tokens."""
+        need = self.needs[group]
+        if not need.forgets or need.keep_first <= 0:
+            return 0
+        return -(-need.keep_first // self.page_size)
 
     # ---- queries ------------------------------------------------------------------------
     def __contains__(self, request_id: str) -> bool:
@@ -190,7 +199,9 @@ class CacheManager:
         for group, pool in enumerate(self.pools):
             table = self.tables[group][held.row]
             first = self._first_live_page(group, held.committed)
-            lacking = [index for index in range(first, page_hi) if table[index] == 0]
+            kept = min(self._kept_pages(group), first)
+            lacking = [index for index in (*range(min(kept, page_hi)), *range(first, page_hi))
+                       if table[index] == 0]
             if len(lacking) > pool.num_free:
                 return False
             plan.append(lacking)
@@ -225,7 +236,8 @@ class CacheManager:
             if not need.forgets:
                 continue
             table = self.tables[group][held.row]
-            for index in range(self._first_live_page(group, before),
+            for index in range(max(self._first_live_page(group, before),
+                                   self._kept_pages(group)),
                                self._first_live_page(group, held.committed)):
                 if table[index]:
                     self.pools[group].give(int(table[index]))
@@ -269,17 +281,18 @@ class CacheManager:
                 row = table[held.row]
                 first = self._first_live_page(group, held.committed)
                 last = -(-(held.committed + held.reserved) // self.page_size)
+                kept = min(self._kept_pages(group), first, last)
                 if held.pages_hi > last:
                     raise EngineError(
                         f"request {request_id!r} counts {held.pages_hi} table entries as "
                         f"filled but its tokens end in page {last}")
                 for index in range(self.max_pages_per_request):
                     page = int(row[index])
-                    if page and not first <= index < max(last, first):
+                    if page and not (first <= index < max(last, first) or index < kept):
                         raise EngineError(
                             f"group {group}: request {request_id!r} holds page {page} at "
                             f"index {index}, outside its live range [{first}, {last})")
-                    if not page and first <= index < last:
+                    if not page and (first <= index < last or index < kept):
                         raise EngineError(
                             f"group {group}: request {request_id!r} lacks a page at index "
                             f"{index}")

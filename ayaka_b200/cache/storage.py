@@ -51,8 +51,43 @@ class CachePlan:
         return sum(self.bytes_per_page(g, itemsize, 1) for g in range(len(self.groups)))
 
 
+def _same_rows(a: CacheNeed, b: CacheNeed) -> bool:
+    """Whether two needs lay a token's rows out alike (how far back they look aside)."""
+    return (a.num_kv_heads, a.head_dim, a.values, a.value_head_dim) == \
+        (b.num_kv_heads, b.head_dim, b.values, b.value_head_dim)
+
+
+def _covering(a: CacheNeed, b: CacheNeed) -> CacheNeed:
+    """The need that keeps every page either of two needs with the same rows still sees."""
+    if a == b:
+        return a
+    window = 0 if (not a.window or not b.window or a.chunk or b.chunk) \
+        else max(a.window, b.window)
+    chunk = a.chunk if a.chunk == b.chunk and not (a.window or b.window) else 0
+    keep_first = max(a.keep_first, b.keep_first) if window else 0
+    return CacheNeed(a.num_kv_heads, a.head_dim, window, a.values, chunk, a.value_dim,
+                     keep_first)
+
+
 def plan_cache(order: tuple[Run, ...],
                needs: list[tuple[CacheNeed | None, StateNeed | None]]) -> CachePlan:
+    """Group the runs by what they need. A run that reads another run's cache shares its
+    slot; it may look back further or less far than the run that writes (a window, kept first
+    tokens of its own): the slot's group then keeps what the furthest-looking of them sees."""
+    owner_need: dict[int, CacheNeed] = {}
+    for index, (run, (need, _)) in enumerate(zip(order, needs)):
+        if need is None:
+            continue
+        if run.reads_cache_of is None:
+            owner_need[index] = need
+            continue
+        owner = run.reads_cache_of
+        if owner not in owner_need or order[owner].reads_cache_of is not None or \
+                not _same_rows(owner_need[owner], need):
+            raise ConfigError(
+                "model.order", "CACHE_MISMATCH",
+                f"run {index} reads the cache of run {owner}, whose geometry differs")
+        owner_need[owner] = _covering(owner_need[owner], need)
     groups: list[CacheNeed] = []
     slots: list[int] = []
     run_group: list[int | None] = []
@@ -66,14 +101,11 @@ def plan_cache(order: tuple[Run, ...],
             continue
         if run.reads_cache_of is not None:
             owner = run.reads_cache_of
-            if run_group[owner] is None or needs[owner][0] != need:
-                raise ConfigError(
-                    "model.order", "CACHE_MISMATCH",
-                    f"run {index} reads the cache of run {owner}, whose geometry differs")
             run_group.append(run_group[owner])
             run_slot.append(run_slot[owner])
             run_writes.append(False)
             continue
+        need = owner_need[index]
         if need not in groups:
             groups.append(need)
             slots.append(0)

@@ -42,9 +42,14 @@ __global__ void latent_prepare_kernel(const float* __restrict__ proj, int ld_pro
   pdl_wait_for(proj);
   const float* src = proj + (size_t)row * ld_proj;
   const float* c_raw = src + kv_offset;
-  float s = 0.f;
-  for (int j = threadIdx.x; j < rank; j += blockDim.x) s += c_raw[j] * c_raw[j];
-  const float inv = 1.f / sqrtf(block_sum(s, scratch) / (float)rank + eps);  // (also a barrier)
+  float inv = 0.f;
+  if (pages != nullptr) {  // (a layer that reads another's latents has no raw latent at all)
+    float s = 0.f;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) s += c_raw[j] * c_raw[j];
+    inv = 1.f / sqrtf(block_sum(s, scratch) / (float)rank + eps);  // (also a barrier)
+  } else {
+    __syncthreads();  // the table of sines is read below
+  }
   if (pages != nullptr && slot >= 0) {
     T* dst = pages + (size_t)slot * (rank + rot);
     for (int j = threadIdx.x; j < rank; j += blockDim.x) {
@@ -747,7 +752,8 @@ AYK_API int ayk_latent_prepare(const float* proj, int ld_proj, int kv_offset,
   using namespace ayk;
   if (rows == 0) return AYK_OK;
   if (rows < 0 || heads < 1 || dim < 0 || rot < 0 || rank < 1 || rot_dims < 0 || rot_dims % 2 ||
-      rot_dims > rot || kv_offset < heads * (dim + rot) || ld_proj < kv_offset + rank + rot ||
+      rot_dims > rot || kv_offset < heads * (dim + rot) || ld_proj < heads * (dim + rot) ||
+      (pages != nullptr && ld_proj < kv_offset + rank + rot) ||
       ld_plain < heads * dim || ld_qa < heads * (rank + rot) || proj == nullptr ||
       latent_weight == nullptr || positions == nullptr || (rot_dims > 0 && freq == nullptr) ||
       q_plain == nullptr || qa == nullptr || !(eps > 0.f) ||

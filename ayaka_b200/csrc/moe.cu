@@ -8,7 +8,8 @@
 //            a multiple of the tile's rows (-1 = no pair), and the expert of every tile;
 //   experts: two grouped products over those tiles. The first computes, per pair,
 //            g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit) and writes
-//            y = g sigmoid(alpha g) (u + 1); the second writes W_down y per pair in fp32;
+//            y = g sigmoid(alpha g) (u + shift); the second writes W_down y per pair in
+//            fp32 (limit = infinity, alpha = 1, shift = 0: silu(g) u);
 //   join:    dst[row] (+)= scale * sum_choice share * (W_down y)[pair], choices in order.
 // A pair's result does not depend on its place in a tile or on the other pairs: every output
 // element is one sum over k in a fixed order. Experts' matrices lie one under the other:
@@ -75,6 +76,98 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, int r
   for (int j = 32 + lane; j < top; j += 32) share[(size_t)row * top + j] /= total;
 }
 
+// Routing by scores with groups: s = sigmoid(logit); the experts form `groups` equal groups of
+// neighbours, a group's score is the sum of its two largest s (its only one when a group is one
+// expert), and only experts of the `keep` best groups can be chosen; of those the `top` largest
+// s are taken (ties to the smaller index, also among groups). share = factor * s, divided by
+// the chosen ones' sum when `renorm` is set. One warp per row; the row's scores, the groups'
+// scores and the kept groups' marks lie in the warp's part of shared memory.
+__global__ void moe_route_scored_kernel(const float* __restrict__ logits, int ld, int rows, int E,
+                                        int top, int groups, int keep, float factor, int renorm,
+                                        int* __restrict__ chosen, float* __restrict__ share) {
+  extern __shared__ float route_smem[];
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  float* s = route_smem + (size_t)warp * (E + 2 * groups);
+  float* gs = s + E;
+  int* kept = reinterpret_cast<int*>(gs + groups);
+  const int per = E / groups;
+  pdl_wait_for(logits);
+  const float* z = logits + (size_t)row * ld;
+  for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-z[e]));
+  __syncwarp();
+  // the largest entry of v[0 .. n) not yet taken (taken ones are -inf), ties to the smaller index
+  auto arg_max = [&](const float* v, int n, float& best, int& at) {
+    best = -INFINITY;
+    at = INT_MAX;
+    for (int i = lane; i < n; i += 32) {
+      if (v[i] > best || at == INT_MAX) {
+        best = v[i];
+        at = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_at = __shfl_xor_sync(0xffffffffu, at, o);
+      if (other_at != INT_MAX && (at == INT_MAX || other > best ||
+                                  (other == best && other_at < at))) {
+        best = other;
+        at = other_at;
+      }
+    }
+  };
+  if (keep < groups) {
+    for (int g = lane; g < groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;
+      for (int i = 0; i < per; ++i) {
+        const float v = s[g * per + i];
+        if (v > a) {
+          b = a;
+          a = v;
+        } else if (v > b) {
+          b = v;
+        }
+      }
+      gs[g] = per > 1 ? a + b : a;
+      kept[g] = 0;
+    }
+    __syncwarp();
+    for (int j = 0; j < keep; ++j) {
+      float best;
+      int at;
+      arg_max(gs, groups, best, at);
+      if (lane == 0) {
+        gs[at] = -INFINITY;
+        kept[at] = 1;
+      }
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) {
+      if (!kept[e / per]) s[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best;
+    int at;
+    arg_max(s, E, best, at);
+    total += best;
+    if (lane == 0) {
+      s[at] = -INFINITY;
+      chosen[(size_t)row * top + j] = at;
+      share[(size_t)row * top + j] = best * factor;
+    }
+    __syncwarp();
+  }
+  if (renorm) {
+    for (int j = lane; j < top; j += 32) share[(size_t)row * top + j] /= total;
+  }
+}
+
 // One CTA. sorted: [max_tiles * tile_rows] pair indices or -1; tile_expert: [max_tiles], -1 for a
 // tile past the last.
 __global__ void __launch_bounds__(1024)
@@ -115,10 +208,10 @@ moe_align_kernel(const int* __restrict__ chosen, int pairs, int E, int max_tiles
 // top), the weight tile is rows n0.. of the expert's gate part and of its up part, the result
 // y[place][n] in the compute type. PHASE 1: rows of `a` are y[place], the weight tile rows
 // n0.. of the expert's down matrix, the result out[pair][n] in fp32.
-__device__ __forceinline__ float expert_unit(float g, float u, float limit, float alpha) {
+__device__ __forceinline__ float expert_unit(float g, float u, float limit, float alpha, float shift) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
-  return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+  return g / (1.f + expf(-alpha * g)) * (u + shift);
 }
 
 template <typename T, int PHASE, int TM> struct TileAcc;
@@ -263,7 +356,7 @@ template <typename T, int PHASE, int TM>
 __global__ void __launch_bounds__(256, 2)  // two CTAs an SM: one's copies under the other's products
 moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
                 const int* __restrict__ sorted, const int* __restrict__ tile_expert, int top,
-                int K, int N, float limit, float alpha, T* __restrict__ y, int ld_y,
+                int K, int N, float limit, float alpha, float shift, T* __restrict__ y, int ld_y,
                 float* __restrict__ out, int ld_out, int wide) {
   using Acc = TileAcc<T, PHASE, TM>;
   constexpr int LDS = Acc::LDS, TK = Acc::TK;
@@ -360,7 +453,7 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
     if (pair < 0 || n0 + c >= N) return;
     if (PHASE == 0) {
       stf(y + ((size_t)tile * TM + r) * ld_y + n0 + c,
-          expert_unit(first, second, limit, alpha));
+          expert_unit(first, second, limit, alpha, shift));
     } else {
       out[(size_t)pair * ld_out + n0 + c] = first;
     }
@@ -389,7 +482,7 @@ __global__ void moe_join_kernel(const float* __restrict__ pair_out, int ld, cons
 template <typename T, int TM>
 int moe_experts(const void* hidden, int ld_hidden, const void* w_in, const void* w_out,
                 const int* sorted, const int* tile_expert, int max_tiles, int top, int width,
-                int ff, float limit, float alpha, void* y, int ld_y, float* pair_out, int ld_out,
+                int ff, float limit, float alpha, float shift, void* y, int ld_y, float* pair_out, int ld_out,
                 cudaStream_t stream) {
   // 16-byte pieces when every row of every operand starts on a 16-byte boundary
   const auto aligned = [](const void* p) { return ((uintptr_t)p % 16) == 0; };
@@ -409,12 +502,12 @@ int moe_experts(const void* hidden, int ld_hidden, const void* w_in, const void*
   const dim3 grid_in(max_tiles, (ff + MOE_TN - 1) / MOE_TN);
   int status = launch_kernel(moe_tile_kernel<T, 0, TM>, grid_in, dim3(256), 0, stream, 1,
                              (const T*)hidden, ld_hidden, (const T*)w_in, sorted, tile_expert,
-                             top, width, ff, limit, alpha, (T*)y, ld_y, (float*)nullptr, 0,
+                             top, width, ff, limit, alpha, shift, (T*)y, ld_y, (float*)nullptr, 0,
                              wide_in);
   if (status != AYK_OK) return status;
   const dim3 grid_out(max_tiles, (width + MOE_TN - 1) / MOE_TN);
   return launch_kernel(moe_tile_kernel<T, 1, TM>, grid_out, dim3(256), 0, stream, 1, (const T*)y,
-                       ld_y, (const T*)w_out, sorted, tile_expert, top, ff, width, limit, alpha,
+                       ld_y, (const T*)w_out, sorted, tile_expert, top, ff, width, limit, alpha, shift,
                        (T*)nullptr, 0, pair_out, ld_out, wide_out);
 }
 
@@ -439,12 +532,33 @@ AYK_API int ayk_moe_route(const float* logits, int ld, int rows, int experts, in
                        (cudaStream_t)stream, 1, logits, ld, rows, experts, top, chosen, share);
 }
 
+// Scores instead of a softmax: see moe_route_scored_kernel. `groups` divides `experts`,
+// 1 <= keep <= groups, and the kept groups hold at least `top` experts.
+AYK_API int ayk_moe_route_scored(const float* logits, int ld, int rows, int experts, int top,
+                                 int groups, int keep, float factor, int renorm, int* chosen,
+                                 float* share, void* stream) {
+  using namespace ayk;
+  if (rows == 0) return AYK_OK;
+  if (rows < 0 || experts < 1 || top < 1 || groups < 1 || experts % groups || keep < 1 ||
+      keep > groups || top > keep * (experts / groups) || ld < experts || logits == nullptr ||
+      chosen == nullptr || share == nullptr) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (experts > MOE_MAX_EXPERTS) return AYK_TOO_LARGE;
+  const int per_warp = experts + 2 * groups;
+  const int warps = per_warp <= 1024 ? 4 : 1;
+  return launch_kernel(moe_route_scored_kernel, dim3((rows + warps - 1) / warps),
+                       dim3(32 * warps), (size_t)warps * per_warp * sizeof(float),
+                       (cudaStream_t)stream, 1, logits, ld, rows, experts, top, groups, keep,
+                       factor, renorm, chosen, share);
+}
+
 // Three launches: align, the two grouped products. `sorted` holds max_tiles * tile_rows ints,
 // `tile_expert` max_tiles, `y` max_tiles * tile_rows rows of ff, `pair_out` rows * top rows
 // of width. type: 0 = float32, 1 = bfloat16. tile_rows: 32, or 128 (bfloat16 only).
 AYK_API int ayk_moe_experts(const void* hidden, int ld_hidden, const void* w_in,
                             const void* w_out, const int* chosen, int rows, int experts, int top,
-                            int width, int ff, float limit, float alpha, int* sorted,
+                            int width, int ff, float limit, float alpha, float shift, int* sorted,
                             int* tile_expert, int max_tiles, int tile_rows, void* y, int ld_y,
                             float* pair_out, int ld_out, int type, void* stream) {
   using namespace ayk;
@@ -466,17 +580,17 @@ AYK_API int ayk_moe_experts(const void* hidden, int ld_hidden, const void* w_in,
   if (status != AYK_OK) return status;
   if (type == 0) {
     return moe_experts<float, MOE_TM>(hidden, ld_hidden, w_in, w_out, sorted, tile_expert, max_tiles,
-                              top, width, ff, limit, alpha, y, ld_y, pair_out, ld_out, s);
+                              top, width, ff, limit, alpha, shift, y, ld_y, pair_out, ld_out, s);
   }
   if (type == 1 && tile_rows == MOE_TM_WIDE) {
     return moe_experts<__nv_bfloat16, MOE_TM_WIDE>(hidden, ld_hidden, w_in, w_out, sorted,
                                                    tile_expert, max_tiles, top, width, ff, limit,
-                                                   alpha, y, ld_y, pair_out, ld_out, s);
+                                                   alpha, shift, y, ld_y, pair_out, ld_out, s);
   }
   if (type == 1) {
     return moe_experts<__nv_bfloat16, MOE_TM>(hidden, ld_hidden, w_in, w_out, sorted,
                                               tile_expert, max_tiles, top, width, ff, limit,
-                                              alpha, y, ld_y, pair_out, ld_out, s);
+                                              alpha, shift, y, ld_y, pair_out, ld_out, s);
   }
   return AYK_BAD_ARGUMENT;
 }

@@ -155,6 +155,30 @@ __global__ void norm_sum_kernel(Branches in, int count, float eps, float factor,
   }
 }
 
+// dst[r][c] += factor * x[r][c] * rsqrt(mean_c(x[r]^2) + eps) * (offset + w[c]), and, when
+// `copy` is given, copy[r][c] = the new dst[r][c] in the compute type: a sublayer's normed
+// result joins the fp32 residual stream and the next sublayer's input leaves the same pass.
+template <typename TOut>
+__global__ void norm_add_kernel(const float* __restrict__ x, int ld_x,
+                                const float* __restrict__ weight, float offset, float eps,
+                                float factor, float* __restrict__ dst, int ld_dst,
+                                TOut* __restrict__ copy, int ld_copy, int width) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  pdl_wait_for(x, dst);
+  const float* src = x + (size_t)r * ld_x;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) s += src[c] * src[c];
+  const float inv = factor / sqrtf(block_sum(s, scratch) / (float)width + eps);
+  float* to = dst + (size_t)r * ld_dst;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to[c] + src[c] * inv * (offset + weight[c]);
+    to[c] = v;
+    if (copy != nullptr) stf(copy + (size_t)r * ld_copy + c, v);
+  }
+}
+
 }  // namespace ayk
 
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
@@ -210,4 +234,26 @@ AYK_API int ayk_scale_add(const float* x, int ld_x, const float* scale, float* d
   }
   return launch_kernel(scale_add_kernel, dim3(n), dim3(width >= 512 ? 256 : 128), 0,
                        (cudaStream_t)stream, 1, x, ld_x, scale, dst, ld_dst, width, accumulate);
+}
+
+// copy_type: 0 = float32, 1 = bfloat16 (ignored when `copy` is null).
+AYK_API int ayk_norm_add(const float* x, int ld_x, const float* weight, float offset, float eps,
+                         float factor, float* dst, int ld_dst, void* copy, int ld_copy,
+                         int copy_type, int n, int width, void* stream) {
+  using namespace ayk;
+  if (n == 0) return AYK_OK;
+  if (n < 0 || width < 1 || x == nullptr || weight == nullptr || dst == nullptr ||
+      ld_x < width || ld_dst < width || (copy != nullptr && ld_copy < width) || !(eps > 0.f)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  if (copy != nullptr && copy_type == 1) {
+    return launch_kernel(norm_add_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0,
+                         (cudaStream_t)stream, 1, x, ld_x, weight, offset, eps, factor, dst,
+                         ld_dst, (__nv_bfloat16*)copy, ld_copy, width);
+  }
+  if (copy != nullptr && copy_type != 0) return AYK_BAD_ARGUMENT;
+  return launch_kernel(norm_add_kernel<float>, dim3(n), dim3(threads), 0, (cudaStream_t)stream,
+                       1, x, ld_x, weight, offset, eps, factor, dst, ld_dst, (float*)copy,
+                       ld_copy, width);
 }

@@ -24,9 +24,13 @@ __all__ = [
     "attention",
     "attention_decode",
     "attention_prefill",
+    "cast_rows",
     "causal_conv_silu",
     "decode_splits",
     "embed_rows",
+    "gated_attention",
+    "gated_attention_prepare",
+    "gated_unit",
     "head_linear",
     "kv_store",
     "latent_attention",
@@ -46,8 +50,10 @@ __all__ = [
     "moe_join",
     "moe_max_tiles",
     "moe_route",
+    "moe_route_scored",
     "moe_scratch",
     "moe_tile_rows",
+    "norm_add",
     "norm_sum",
     "rms_norm",
     "rope",
@@ -822,7 +828,8 @@ def latent_prepare(proj: torch.Tensor, *, kv_offset: int, latent_weight: torch.T
     ``rot``): the latent normalised by its root mean square times ``latent_weight`` and the
     rotated key piece go to the row's cache slot (``pages`` ``[page, 1, slot, rank + rot]``),
     the unrotated query parts to ``q_plain`` ``[N, heads * dim]``, the rotated ones to
-    ``qa[:, h, rank:]`` (``qa`` is ``[N, heads * (rank + rot)]``)."""
+    ``qa[:, h, rank:]`` (``qa`` is ``[N, heads * (rank + rot)]``). Without ``pages`` (a layer
+    that reads latents another layer stored) the columns from ``kv_offset`` on are not read."""
     op = "latent_prepare"
     if _left_out and op in _left_out:
         return
@@ -844,7 +851,8 @@ def latent_prepare(proj: torch.Tensor, *, kv_offset: int, latent_weight: torch.T
     if rows > proj.shape[0] or rows > positions.shape[0] or rows > q_plain.shape[0] or \
             rows > qa.shape[0] or latent_weight.shape[0] != rank or \
             q_plain.shape[1] != heads * dim or qa.shape[1] != heads * (rank + rot) or \
-            proj.shape[1] < kv_offset + rank + rot or \
+            (pages is not None and proj.shape[1] < kv_offset + rank + rot) or \
+            proj.shape[1] < heads * (dim + rot) or \
             (slot_mapping is not None and rows > slot_mapping.shape[0]):
         raise BackendError(f"{op}: shapes do not fit")
     status = library("latent_attention").ayk_latent_prepare(
@@ -1368,13 +1376,14 @@ def moe_route(logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, *
 def moe_experts(hidden: torch.Tensor, w_in: torch.Tensor, w_out: torch.Tensor,
                 chosen: torch.Tensor, pair_out: torch.Tensor, *, experts: int, top: int,
                 limit: float, alpha: float, sorted_pairs: torch.Tensor,
-                tile_expert: torch.Tensor, inner: torch.Tensor, rows: int) -> None:
+                tile_expert: torch.Tensor, inner: torch.Tensor, rows: int,
+                shift: float = 1.0) -> None:
     """The chosen experts of every row, as two products grouped by expert. ``w_in``
     ``[experts * 2 * ff, width]`` holds each expert's gate rows, then its up rows; ``w_out``
     ``[experts * width, ff]`` its down matrix. Pair ``p = row * top + choice`` computes
     ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -limit, limit)``,
-    ``y = g * sigmoid(alpha * g) * (u + 1)`` and ``pair_out[p] = W_down y`` (float32
-    ``[N * top, width]``, unweighted). Scratch: ``sorted_pairs`` (int32, ``tiles * tile
+    ``y = g * sigmoid(alpha * g) * (u + shift)`` and ``pair_out[p] = W_down y`` (float32
+    ``[N * top, width]``, unweighted); ``limit=inf, alpha=1, shift=0`` is ``silu(g) * u``. Scratch: ``sorted_pairs`` (int32, ``tiles * tile
     rows``), ``tile_expert`` (int32, ``tiles``) and ``inner`` (``[tiles * tile rows, ff]``,
     compute dtype) sized by :func:`moe_scratch`."""
     op = "moe_experts"
@@ -1404,7 +1413,8 @@ def moe_experts(hidden: torch.Tensor, w_in: torch.Tensor, w_out: torch.Tensor,
     status = library("moe").ayk_moe_experts(
         _ptr(hidden), c_int(hidden.stride(0)), _ptr(w_in), _ptr(w_out), _ptr(chosen),
         c_int(rows), c_int(experts), c_int(top), c_int(width), c_int(ff), c_float(limit),
-        c_float(alpha), _ptr(sorted_pairs), _ptr(tile_expert), c_int(tiles), c_int(tile_rows),
+        c_float(alpha), c_float(shift), _ptr(sorted_pairs), _ptr(tile_expert), c_int(tiles),
+        c_int(tile_rows),
         _ptr(inner),
         c_int(inner.stride(0)), _ptr(pair_out), c_int(pair_out.stride(0)),
         c_int(_TYPE[hidden.dtype]), _stream())
@@ -1433,4 +1443,208 @@ def moe_join(pair_out: torch.Tensor, share: torch.Tensor, dst: torch.Tensor, *, 
         _ptr(pair_out), c_int(pair_out.stride(0)), _ptr(share), c_int(rows), c_int(top),
         _ptr(scale), _ptr(dst), c_int(dst.stride(0)), c_int(width),
         c_int(1 if accumulate else 0), _stream())
+    check(status, op)
+
+
+def moe_route_scored(logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, *,
+                     top: int, groups: int = 1, keep: int = 1, factor: float = 1.0,
+                     renormalise: bool = False, rows: int) -> None:
+    """Routing by scores ``s = sigmoid(logits)`` (float32 ``[N, experts]``): the experts form
+    ``groups`` equal groups of neighbours, a group's score is the sum of its two largest ``s``,
+    only experts of the ``keep`` best groups can be chosen, and of those the ``top`` largest
+    are (ties to the smaller index), in descending order, into ``chosen`` (int32 ``[N * top]``).
+    ``share`` (float32 ``[N * top]``) gets ``factor * s``, divided by the chosen ones' sum
+    with ``renormalise``."""
+    op = "moe_route_scored"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "logits", logits, torch.float32, 2)
+    _need(op, "chosen", chosen, torch.int32, 1)
+    _need(op, "share", share, torch.float32, 1)
+    if rows > logits.shape[0] or min(chosen.shape[0], share.shape[0]) < rows * top:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("moe").ayk_moe_route_scored(
+        _ptr(logits), c_int(logits.stride(0)), c_int(rows), c_int(logits.shape[1]), c_int(top),
+        c_int(groups), c_int(keep), c_float(factor), c_int(1 if renormalise else 0),
+        _ptr(chosen), _ptr(share), _stream())
+    check(status, op)
+
+
+# ---- sublayers that read the residual stream itself, gated units ----------------------------
+
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor, *, rows: int) -> None:
+    """``out = x`` (float32 ``[N, width]``) in ``out``'s type (float32 or bfloat16)."""
+    op = "cast_rows"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "x", x, torch.float32, 2)
+    _need(op, "out", out, ndim=2)
+    if out.dtype not in _TYPE or out.shape[1] != x.shape[1] or rows > x.shape[0] or \
+            rows > out.shape[0]:
+        raise BackendError(f"{op}: shapes or types do not fit")
+    status = library("gated").ayk_cast_rows(
+        _ptr(x), c_int(x.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(rows),
+        c_int(x.shape[1]), c_int(_TYPE[out.dtype]), _stream())
+    check(status, op)
+
+
+def gated_unit(gate: torch.Tensor, out: torch.Tensor, *, activation: str, rows: int,
+               other: torch.Tensor | None = None, table: torch.Tensor | None = None,
+               index: torch.Tensor | None = None, column: int = 0) -> None:
+    """``out = act(gate) * other`` entry by entry in fp32 (``act``: ``silu`` or ``gelu_tanh``;
+    ``gate`` and ``other`` float32 ``[N, width]``), or, with ``table`` (``out``'s type) and
+    ``index`` (int32 per row), ``out[r] = act(gate[r]) * table[index[r], column : column +
+    width]``."""
+    op = "gated_unit"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "gate", gate, torch.float32, 2)
+    _need(op, "out", out, ndim=2)
+    width = out.shape[1]
+    if out.dtype not in _TYPE or activation not in GATE_ACTIVATIONS or gate.shape[1] != width \
+            or rows > gate.shape[0] or rows > out.shape[0] or (other is None) == (table is None):
+        raise BackendError(f"{op}: shapes, types or arguments do not fit")
+    if other is not None:
+        _need(op, "other", other, torch.float32, 2)
+        if other.shape[1] != width or rows > other.shape[0]:
+            raise BackendError(f"{op}: other does not match gate")
+    else:
+        _need(op, "table", table, out.dtype, 2)
+        _need(op, "index", index, torch.int32, 1)
+        if column < 0 or table.shape[1] < column + width or rows > index.shape[0]:
+            raise BackendError(f"{op}: the table has no such columns")
+    status = library("gated").ayk_gated_unit(
+        _ptr(gate), c_int(gate.stride(0)), _ptr(other),
+        c_int(0 if other is None else other.stride(0)), _ptr(table),
+        c_int(0 if table is None else table.stride(0)), _ptr(index),
+        c_int(0 if table is None else table.shape[0]), c_int(column),
+        c_int(GATE_ACTIVATIONS[activation]), _ptr(out), c_int(out.stride(0)), c_int(rows),
+        c_int(width), c_int(_TYPE[out.dtype]), _stream())
+    check(status, op)
+
+
+def norm_add(x: torch.Tensor, weight: torch.Tensor, eps: float, dst: torch.Tensor, *,
+             factor: float = 1.0, weight_offset: float = 0.0, copy: torch.Tensor | None = None,
+             rows: int) -> None:
+    """``dst += factor * x * rsqrt(mean(x^2) + eps) * (weight_offset + weight)`` over float32
+    rows; with ``copy`` (float32 or bfloat16 ``[N, width]``) the new ``dst`` is also written
+    there, rounded once."""
+    op = "norm_add"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "x", x, torch.float32, 2)
+    _need(op, "weight", weight, torch.float32, 1)
+    _need(op, "dst", dst, torch.float32, 2)
+    width = dst.shape[1]
+    if x.shape[1] != width or weight.shape[0] != width or rows > x.shape[0] or \
+            rows > dst.shape[0]:
+        raise BackendError(f"{op}: shapes do not fit")
+    if copy is not None:
+        _need(op, "copy", copy, ndim=2)
+        if copy.dtype not in _TYPE or copy.shape[1] != width or rows > copy.shape[0]:
+            raise BackendError(f"{op}: the copy does not match dst")
+    status = library("rms_norm").ayk_norm_add(
+        _ptr(x), c_int(x.stride(0)), _ptr(weight), c_float(weight_offset), c_float(eps),
+        c_float(factor), _ptr(dst), c_int(dst.stride(0)), _ptr(copy),
+        c_int(0 if copy is None else copy.stride(0)),
+        c_int(0 if copy is None else _TYPE[copy.dtype]), c_int(rows), c_int(width), _stream())
+    check(status, op)
+
+
+# ---- attention with a window that keeps the first tokens, and an output gate ----------------
+
+def gated_attention_prepare(proj: torch.Tensor, *, k_offset: int, v_offset: int,
+                            q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+                            eps: float, slot_mapping: torch.Tensor | None,
+                            k_pages: torch.Tensor | None, v_pages: torch.Tensor | None,
+                            q: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                            rows: int) -> None:
+    """From a row of a fused projection (float32: ``heads * dim`` queries at 0, ``kv_heads *
+    dim`` keys at ``k_offset``, ``kv_heads * vdim`` values at ``v_offset``): queries and keys
+    each normalised by the root mean square over their whole projection with a weight per
+    entry (``None``: no norm), the queries written to ``q`` ``[N, heads * dim]``, the key and
+    value into the row's cache slot (``k_pages`` ``[page, kv_head, slot, dim]``, ``v_pages``
+    likewise with ``vdim``; ``None``: stored nowhere)."""
+    op = "gated_attention_prepare"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "proj", proj, torch.float32, 2)
+    _need(op, "q", q, ndim=2)
+    if q.dtype not in _TYPE:
+        raise BackendError(f"{op}: float32 or bfloat16 only")
+    for name, tensor, size in (("q_weight", q_weight, heads * dim),
+                               ("k_weight", k_weight, kv_heads * dim)):
+        if tensor is not None:
+            _need(op, name, tensor, torch.float32)
+            if tensor.numel() != size or not tensor.is_contiguous():
+                raise BackendError(f"{op}: {name} must hold {size} contiguous entries")
+    page_size = 1
+    if k_pages is not None:
+        if v_pages is None or slot_mapping is None:
+            raise BackendError(f"{op}: key pages come with value pages and a slot mapping")
+        _need(op, "k_pages", k_pages, q.dtype, 4)
+        _need(op, "v_pages", v_pages, q.dtype, 4)
+        _need(op, "slot_mapping", slot_mapping, torch.int32, 1)
+        page_size = k_pages.shape[2]
+        if tuple(k_pages.shape[1:]) != (kv_heads, page_size, dim) or \
+                tuple(v_pages.shape[1:]) != (kv_heads, page_size, vdim) or \
+                not k_pages.is_contiguous() or not v_pages.is_contiguous() or \
+                rows > slot_mapping.shape[0]:
+            raise BackendError(f"{op}: pages must be contiguous [page, kv_head, slot, dim]")
+    if rows > proj.shape[0] or rows > q.shape[0] or q.shape[1] != heads * dim or \
+            proj.shape[1] < v_offset + kv_heads * vdim:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("gated_attention").ayk_gated_prepare(
+        _ptr(proj), c_int(proj.stride(0)), c_int(k_offset), c_int(v_offset), _ptr(q_weight),
+        _ptr(k_weight), c_float(eps), _ptr(slot_mapping if k_pages is not None else None),
+        _ptr(k_pages), _ptr(v_pages), c_int(page_size), _ptr(q), c_int(q.stride(0)),
+        c_int(rows), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim),
+        c_int(_TYPE[q.dtype]), _stream())
+    check(status, op)
+
+
+def gated_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                    block_table: torch.Tensor, request_of_row: torch.Tensor,
+                    positions: torch.Tensor, out: torch.Tensor, *, heads: int, scale: float,
+                    window: int = 0, keep_first: int = 0, gate: torch.Tensor | None = None,
+                    rows: int | None = None, tensor_cores: bool = True) -> None:
+    """Softmax attention over paged keys (``[page, kv_head, slot, dim]``) and values (``[...,
+    vdim]``): the row of request ``request_of_row[i]`` at ``positions[i]`` sees key ``j <= p``
+    when ``p - j < window`` (``window`` 0: always) or ``j < keep_first``; head ``h`` uses
+    key/value head ``h // (heads / kv_heads)``; scores ``scale * q . k`` and the softmax in
+    fp32; with ``gate`` (float32 ``[N, heads * vdim]``) the result is multiplied entry by
+    entry by ``sigmoid(gate)``. The step's own keys must already be stored."""
+    op = "gated_attention"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "q", q, ndim=2)
+    _need(op, "out", out, q.dtype, 2)
+    _need(op, "k_pages", k_pages, q.dtype, 4)
+    _need(op, "v_pages", v_pages, q.dtype, 4)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "request_of_row", request_of_row, torch.int32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    if q.dtype not in _TYPE or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise BackendError(f"{op}: contiguous float32 or bfloat16 pages only")
+    _, kv_heads, page_size, dim = k_pages.shape
+    vdim = v_pages.shape[3]
+    n = q.shape[0] if rows is None else rows
+    if q.shape[1] != heads * dim or out.shape[1] != heads * vdim or \
+            tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3]) or n > out.shape[0] or \
+            n > request_of_row.shape[0] or n > positions.shape[0] or heads % kv_heads:
+        raise BackendError(f"{op}: shapes do not fit")
+    if gate is not None:
+        _need(op, "gate", gate, torch.float32, 2)
+        if gate.shape[1] != heads * vdim or gate.shape[0] < n:
+            raise BackendError(f"{op}: the gate does not match the rows")
+    status = library("gated_attention").ayk_gated_attention(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+        c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions), _ptr(gate),
+        c_int(0 if gate is None else gate.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(n),
+        c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(page_size),
+        c_float(scale), c_int(window), c_int(keep_first), c_int(1 if tensor_cores else 0),
+        c_int(_TYPE[q.dtype]), _stream())
     check(status, op)

@@ -86,6 +86,7 @@ class DecoderModel(Part):
         residual = step.workspace.buffer("model.residual", spec.hidden_size, torch.float32)
         self.embedding.forward(  # type: ignore[attr-defined]
             step, residual, self.position.added_rows(step))  # type: ignore[attr-defined]
+        step.extra.pop("block.stream_copy", None)  # (a block's copy of an earlier stream)
         runs = self._native_runs(step, caches) if ops.NATIVE_STEP else None
         if runs is not None:
             # every layer can run from the C++ host code: one call walks the whole order

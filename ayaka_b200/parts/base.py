@@ -45,6 +45,7 @@ class CacheNeed:
     values: bool = True  # False: one row per token only (a latent cache): no value pages
     chunk: int = 0  # n > 0: only keys of the query's own block of n positions (from 0)
     value_dim: int = 0  # entries of a value row when they differ from a key's (0: head_dim)
+    keep_first: int = 0  # with a window: the first n keys of the sequence stay in sight
 
     @property
     def value_head_dim(self) -> int:
@@ -108,13 +109,13 @@ class Part:
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Part]]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {},
-    "head": {},
+    "head": {}, "side": {},
 }
 
 
 def register_part(family: str, kind: str) -> Callable[[Callable[..., Part]], Callable[..., Part]]:
     """Class decorator: make ``kind`` buildable in ``family`` (``mixer``, ``feed_forward``,
-    ``norm``, ``position``, ``block``, ``embedding``, ``head``). Registering a kind again
+    ``norm``, ``position``, ``block``, ``embedding``, ``head``, ``side``). Registering a kind again
     replaces it, so a test may define a toy part without touching the package."""
     if family not in _REGISTRIES:
         raise ConfigError("parts.family", "INVALID_CHOICE",

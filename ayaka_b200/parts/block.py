@@ -9,7 +9,7 @@ from ayaka_b200.parts.base import BuildContext, Part, build_part, register_part
 from ayaka_b200.parts.context import LayerCache, StepContext, Workspace
 from ayaka_b200.parts.spec import LayerSpec
 
-__all__ = ["Block", "ParallelBlock", "PreNormBlock"]
+__all__ = ["Block", "OutputNormBlock", "ParallelBlock", "PreNormBlock"]
 
 
 class Block(Part):
@@ -150,3 +150,68 @@ def _plain_norm(norm: Part | None) -> bool:
     """Whether ``norm`` declares itself a LayerNorm that a fused kernel can apply from its
     (weight, bias, eps); see ``parts/norm.py``."""
     return bool(getattr(norm, "fusable_layer_norm", False))
+
+
+@register_part("block", "output_norm")
+class OutputNormBlock(Block):
+    """``x += f * norm1(mixer(x)); x += f * norm2(feed_forward(x))`` and, with a ``side``
+    part, ``x += f * side(x)``: the norms stand on the sublayers' *outputs*, the sublayers
+    read the residual stream itself, and ``f`` is ``spec.residual_factor``.
+
+    The stream is fp32; a sublayer's matrix operand is its rounding to the compute type, kept
+    in one scratch tensor that every kernel which updates the stream also refreshes
+    (``ops.norm_add`` with ``copy``), so only a model's first layer pays a pass of its own for
+    it. In float32 the sublayers read the stream directly. A sublayer writes into a scratch
+    branch (``forward_into`` where the part has it, else a zeroed branch it adds into)."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext, position: Part | None) -> None:
+        super().__init__(ctx)
+        self.mixer_norm = self.add_child(
+            "mixer_norm", build_part("norm", spec.mixer_norm.kind, spec.mixer_norm, ctx))
+        self.mixer = self.add_child(
+            "mixer", build_part("mixer", spec.mixer.kind, spec.mixer, ctx, position))
+        self.feed_forward_norm = None if spec.feed_forward.kind == "none" else self.add_child(
+            "feed_forward_norm",
+            build_part("norm", spec.feed_forward_norm.kind, spec.feed_forward_norm, ctx))
+        self.feed_forward = self.add_child(
+            "feed_forward",
+            build_part("feed_forward", spec.feed_forward.kind, spec.feed_forward, ctx))
+        self.side = None if spec.side is None else self.add_child(
+            "side", build_part("side", spec.side.kind, spec.side, ctx))
+        self.width = int(spec.mixer_norm.width)  # type: ignore[arg-type]
+        self.factor = float(spec.residual_factor)
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError("an output_norm block needs norms that can add their result "
+                                 "to the stream (add_normed)")
+
+    def forward(self, residual: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
+        n, work = step.num_rows, step.workspace
+        rounded = self.ctx.dtype != torch.float32
+        if rounded:
+            stream = work.buffer("block.stream", self.width, self.ctx.dtype)
+            if not step.extra.get("block.stream_copy"):
+                ops.cast_rows(residual, stream, rows=n)
+            step.extra["block.stream_copy"] = True
+        else:
+            stream = residual
+        copy = stream if rounded else None
+        branch = work.buffer("block.branch", self.width, torch.float32)
+        if hasattr(self.mixer, "forward_into"):
+            self.mixer.forward_into(stream, branch, step, cache)  # type: ignore[attr-defined]
+        else:
+            branch[:n].zero_()
+            self.mixer.forward(stream, branch, step, cache)  # type: ignore[attr-defined]
+        self.mixer_norm.add_normed(branch, residual, factor=self.factor,  # type: ignore
+                                   count=n, copy=copy)
+        if self.feed_forward_norm is not None:
+            if hasattr(self.feed_forward, "forward_into"):
+                self.feed_forward.forward_into(stream, branch, step)  # type: ignore
+            else:
+                branch[:n].zero_()
+                self.feed_forward.forward(stream, branch, step)  # type: ignore[attr-defined]
+            self.feed_forward_norm.add_normed(branch, residual,  # type: ignore[attr-defined]
+                                              factor=self.factor, count=n, copy=copy)
+        if self.side is not None:
+            self.side.forward(stream, residual, step, factor=self.factor,  # type: ignore
+                              copy=copy)

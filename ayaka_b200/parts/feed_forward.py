@@ -9,7 +9,7 @@ from ayaka_b200.parts.base import BuildContext, Part, register_part
 from ayaka_b200.parts.context import StepContext, Workspace
 from ayaka_b200.parts.spec import PartSpec
 
-__all__ = ["DenseMLP", "FeedForward", "NoFeedForward"]
+__all__ = ["DenseMLP", "FeedForward", "GatedMLP", "NoFeedForward"]
 
 
 class FeedForward(Part):
@@ -95,3 +95,41 @@ class DenseMLP(FeedForward):
                           self.up_weight, self.up_bias, inner, scratch=scratch, count=n,
                           activation=self.activation)
         ops.linear(inner, self.down_weight, self.down_bias, residual, residual=True, rows=n)
+
+
+@register_part("feed_forward", "gated_dense")
+class GatedMLP(FeedForward):
+    """``W_down (act(W_gate h) * (W_up h))`` without biases; the unit is evaluated in fp32.
+
+    Parameters: ``in.weight`` ``[2 * inner, width]`` (the gate rows, then the up rows: one
+    product), ``out.weight`` ``[width, inner]``.
+
+    Spec parameters: ``width``, ``inner``, ``activation`` (``silu`` or ``gelu_tanh``).
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
+        super().__init__(ctx)
+        self.width = int(spec.width)  # type: ignore[arg-type]
+        self.inner = int(spec.inner)  # type: ignore[arg-type]
+        self.activation = str(spec.get("activation", "silu"))
+        if self.inner < 1 or self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError("a gated feed-forward needs inner >= 1 and a known activation")
+        self.in_weight = self.add_param("in.weight", (2 * self.inner, self.width), "matrix")
+        self.out_weight = self.add_param("out.weight", (self.width, self.inner), "matrix")
+
+    def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext) -> None:
+        self._run(hidden, residual, step, accumulate=True)
+
+    def forward_into(self, hidden: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        """The same, written into ``out`` (fp32 ``[N, width]``) instead of added to it."""
+        self._run(hidden, out, step, accumulate=False)
+
+    def _run(self, hidden: torch.Tensor, out: torch.Tensor, step: StepContext,
+             accumulate: bool) -> None:
+        n, work = step.num_rows, step.workspace
+        both = work.buffer("gated_dense.both", 2 * self.inner, torch.float32)
+        unit = work.buffer("gated_dense.unit", self.inner, self.ctx.dtype)
+        ops.linear(hidden, self.in_weight, None, both, rows=n)
+        ops.gated_unit(both[:, :self.inner], unit, activation=self.activation, rows=n,
+                       other=both[:, self.inner:])
+        ops.linear(unit, self.out_weight, None, out, residual=accumulate, rows=n)

@@ -62,3 +62,11 @@ class RMSNorm(Part):
         """Normalise ``count`` fp32 rows of ``x`` (gathered by ``rows`` if given) into ``out``."""
         ops.rms_norm(x, self.weight, self.eps, out, weight_offset=self.offset, rows=rows,
                      count=count)
+
+    def add_normed(self, x: torch.Tensor, residual: torch.Tensor, *, factor: float, count: int,
+                   copy: torch.Tensor | None = None) -> None:
+        """``residual += factor * norm(x)`` over ``count`` fp32 rows (a norm on a sublayer's
+        *output*); with ``copy`` the new rows of the stream are also written there in its
+        type, for the sublayer that reads them next."""
+        ops.norm_add(x, self.weight, self.eps, residual, factor=factor,
+                     weight_offset=self.offset, copy=copy, rows=count)

@@ -67,6 +67,10 @@ class LayerSpec:
     #: each half's result is multiplied element by element by a learned vector of the model's
     #: width before it joins the residual stream (blocks that know of it declare the vectors)
     layer_scale: bool = False
+    #: a factor on everything a sublayer adds to the residual stream (blocks that know of it)
+    residual_factor: float = 1.0
+    #: a part of family ``side`` that runs after the feed-forward and adds to the stream too
+    side: PartSpec | None = None
 
 
 @dataclass(frozen=True, slots=True)
