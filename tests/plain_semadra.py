@@ -11,8 +11,9 @@ import math
 
 import torch
 
-__all__ = ["attention_layer", "dense", "expert_choice", "forward", "gelu_tanh", "latent",
-           "latent_attention_layer", "mixture", "rms", "side_input", "visible", "softmax_attention"]
+__all__ = ["attention_layer", "cast_state", "dense", "expert_choice", "forward", "gelu_tanh",
+           "greedy_generate", "latent", "latent_attention_layer", "logits", "mixture", "rms",
+           "router_margins", "side_input", "softmax_attention", "visible"]
 
 F64 = torch.float64
 
@@ -61,7 +62,8 @@ def attention_layer(h: torch.Tensor, w: dict[str, torch.Tensor], p: str, mixer: 
     q = rms(h @ w[p + "q"].T, eps) * w[p + "q.norm"]
     k = rms(h @ w[p + "k"].T, eps) * w[p + "k.norm"]
     v = h @ w[p + "v"].T
-    mask = visible(length, mixer["mask"]["size"], mixer["mask"].get("keep_first", 0))
+    mask = visible(length, (mixer.get("mask") or {}).get("size") or length,
+                   (mixer.get("mask") or {}).get("keep_first", 0))
     joined = softmax_attention(q.view(length, heads, dim), k.view(length, groups, dim),
                                v.view(length, groups, vdim), mixer["scale"], mask)
     return (joined * torch.sigmoid(h @ w[p + "g"].T)) @ w[p + "o"].T
@@ -80,7 +82,8 @@ def latent_attention_layer(h: torch.Tensor, c: torch.Tensor, w: dict[str, torch.
     q = (cq @ w[p + "uq"].T).view(length, heads, dim)
     k = (c @ w[p + "uk"].T).view(length, heads, dim)
     v = (c @ w[p + "uv"].T).view(length, heads, vdim)
-    joined = softmax_attention(q, k, v, mixer["scale"], visible(length, mixer["mask"]["size"]))
+    joined = softmax_attention(q, k, v, mixer["scale"],
+                               visible(length, (mixer.get("mask") or {}).get("size") or length))
     return joined @ w[p + "o"].T
 
 
@@ -102,11 +105,34 @@ def expert_choice(scores: torch.Tensor, top: int, count: int, keep: int) -> torc
     return scores.masked_fill(~allowed, -math.inf).topk(top, dim=-1).indices
 
 
-def mixture(h: torch.Tensor, w: dict[str, torch.Tensor], p: str, mlp: dict) -> torch.Tensor:
+def choice_margin(scores: torch.Tensor, top: int, count: int, keep: int) -> torch.Tensor:
+    """Per row, how close the choice was: the smaller of the gap between the last kept and the
+    first dropped group's score and the gap between the last chosen and the first unchosen
+    score among the kept groups' experts (scores lie in (0, 1))."""
+    length, experts = scores.shape
+    margin = torch.full((length,), float("inf"), dtype=scores.dtype)
+    grouped = scores.view(length, count, experts // count)
+    group_score = grouped.topk(min(2, experts // count), dim=-1).values.sum(-1)
+    if keep < count:
+        ordered = group_score.sort(dim=-1, descending=True).values
+        margin = torch.minimum(margin, ordered[:, keep - 1] - ordered[:, keep])
+    best = group_score.topk(keep, dim=-1).indices
+    allowed = torch.zeros(length, count, dtype=torch.bool).scatter_(1, best, True)
+    allowed = allowed[:, :, None].expand_as(grouped).reshape(length, experts)
+    ordered = scores.masked_fill(~allowed, -1.0).sort(dim=-1, descending=True).values
+    if top < experts and top < keep * (experts // count):
+        margin = torch.minimum(margin, ordered[:, top - 1] - ordered[:, top])
+    return margin
+
+
+def mixture(h: torch.Tensor, w: dict[str, torch.Tensor], p: str, mlp: dict,
+            margins: list[torch.Tensor] | None = None) -> torch.Tensor:
     router = mlp["router"]
     scores = torch.sigmoid(h @ w[p + "router"].T)
     groups = router.get("groups") or {"count": 1, "keep": 1}
     chosen = expert_choice(scores, router["top"], groups["count"], groups["keep"])
+    if margins is not None:
+        margins.append(choice_margin(scores, router["top"], groups["count"], groups["keep"]))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
@@ -125,13 +151,14 @@ def side_input(x: torch.Tensor, tokens: torch.Tensor, w: dict[str, torch.Tensor]
 
 
 def forward(config: dict, weights: dict[str, torch.Tensor], tokens: list[int],
-            layers_out: list[torch.Tensor] | None = None) -> torch.Tensor:
+            layers_out: list[torch.Tensor] | None = None,
+            margins: list[torch.Tensor] | None = None) -> torch.Tensor:
     """Logits ``[T, vocab]`` of one sequence; ``layers_out`` collects the residual stream after
-    every layer."""
+    every layer, ``margins`` every router's closeness of choice."""
     w = {name: t.to(F64) if t.is_floating_point() else t for name, t in weights.items()}
-    eps, m = config["norm"]["eps"], config["residual_mult"]
-    ids = torch.tensor(tokens, dtype=torch.long)
-    x = w["embed"][ids] * config["embedding"]["scale"]
+    eps, m = config["norm"]["eps"], config.get("residual_mult", 1.0)
+    ids = torch.as_tensor(tokens, dtype=torch.long)
+    x = w["embed"][ids] * (config.get("embedding") or {}).get("scale", 1.0)
     latents: dict[int, torch.Tensor] = {}
     side = config.get("token_side")
     for i, layer in enumerate(config["layers"]):
@@ -147,7 +174,8 @@ def forward(config: dict, weights: dict[str, torch.Tensor], tokens: list[int],
         x = x + m * rms(y, eps) * (1.0 + w[p + "norm1"])
         mlp = layer.get("mlp")
         if mlp is not None:
-            y = dense(x, w, p + "mlp.") if mlp["kind"] == "dense" else mixture(x, w, p + "mlp.", mlp)
+            y = dense(x, w, p + "mlp.") if mlp["kind"] == "dense" \
+                else mixture(x, w, p + "mlp.", mlp, margins)
             x = x + m * rms(y, eps) * (1.0 + w[p + "norm2"])
         if side is not None:
             x = x + m * side_input(x, ids, w, p + "side.", i, side["dim"], eps)
@@ -155,3 +183,32 @@ def forward(config: dict, weights: dict[str, torch.Tensor], tokens: list[int],
             layers_out.append(x.clone())
     x = rms(x, eps) * (1.0 + w["final.norm"])
     return x @ w["embed"].T
+
+
+def cast_state(state: dict, dtype: torch.dtype) -> dict:
+    return {name: t.to(dtype) if t.is_floating_point() else t for name, t in state.items()}
+
+
+def logits(state: dict, config: dict, tokens: torch.Tensor) -> torch.Tensor:
+    return forward(config, state, tokens)
+
+
+def router_margins(state: dict, config: dict, tokens: torch.Tensor) -> torch.Tensor:
+    """Per position, the smallest closeness of choice over the layers' routers. Where it is
+    below the rounding of an engine's arithmetic the model is discontinuous: another expert
+    may rightly be chosen there, and the logits jump."""
+    margins: list[torch.Tensor] = []
+    forward(config, state, tokens, margins=margins)
+    out = torch.full((len(tokens),), float("inf"), dtype=F64)
+    for margin in margins:
+        out = torch.minimum(out, margin)
+    return out
+
+
+def greedy_generate(state: dict, config: dict, prompt: list[int], count: int) -> list[int]:
+    """``count`` tokens, each the largest logit (smallest id on ties) of the whole sequence
+    so far run from scratch."""
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(int(torch.argmax(forward(config, state, tokens)[-1])))
+    return tokens[len(prompt):]
