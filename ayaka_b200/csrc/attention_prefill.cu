@@ -11,7 +11,13 @@
 //
 // The rows of a step are the last rows[b] positions of each request b (row_start/kv_len);
 // tiles of all requests are numbered consecutively along grid.x and each CTA finds its own.
-// Compiled for one head size: -DAYK_HEAD_DIM=<multiple of 16, at most 256>.
+// Compiled for one head size: -DAYK_HEAD_DIM=<multiple of 16, at most 256>, and, where value
+// rows have a size of their own, -DAYK_VALUE_DIM=<likewise>.
+//
+// Options of a launch: `window` (a row at position p sees keys j > p - window), `keep_first`
+// (with a window: keys j < keep_first stay visible to every later row; the blocks that hold
+// them are walked first, then the window's, so the walk still depends on positions alone) and
+// `gate` (fp32, one raw gate per output entry: the result is multiplied by its sigmoid).
 //
 // This kernel uses the legacy warp-level tensor path (not tcgen05): attention is ~5% of a
 // prefill step's FLOPs and this dataflow is proven; the matrix products that dominate run on
@@ -20,6 +26,9 @@
 
 #ifndef AYK_HEAD_DIM
 #define AYK_HEAD_DIM 64
+#endif
+#ifndef AYK_VALUE_DIM
+#define AYK_VALUE_DIM AYK_HEAD_DIM
 #endif
 
 namespace ayk {
@@ -30,8 +39,15 @@ constexpr int PF_BN = 64;               // keys per block
 constexpr int PF_STRIDE = PF_HD + 8;    // elements per shared row: one 16-byte chunk of padding
 constexpr int PF_TILE = PF_BM * PF_STRIDE;  // elements of one [64][HD] tile
 constexpr int PF_CHUNKS = PF_HD / 8;    // 16-byte chunks per row
-constexpr int PF_SMEM_BYTES = 5 * PF_TILE * 2;  // Q, 2 x K, 2 x V
+constexpr int PF_VD = AYK_VALUE_DIM;    // entries of a value row
+constexpr int PF_VSTRIDE = PF_VD + 8;
+constexpr int PF_VTILE = PF_BN * PF_VSTRIDE;
+constexpr int PF_VCHUNKS = PF_VD / 8;
+// the queries' tile is the output's staging space afterwards: room for the larger of the two
+constexpr int PF_QTILE = PF_TILE > PF_VTILE ? PF_TILE : PF_VTILE;
+constexpr int PF_SMEM_BYTES = (PF_QTILE + 2 * PF_TILE + 2 * PF_VTILE) * 2;  // Q, 2 x K, 2 x V
 static_assert(PF_HD % 16 == 0 && PF_HD >= 16 && PF_HD <= 256, "head size");
+static_assert(PF_VD % 16 == 0 && PF_VD >= 16 && PF_VD <= 256, "value size");
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -69,18 +85,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Gather one block of 64 keys (or values) of one head into a [64][HD] shared tile.
+// Gather one block of 64 keys (or values) of one head into a [64][D] shared tile.
+template <int D>
 __device__ __forceinline__ void load_kv_block(__nv_bfloat16* tile,
                                               const __nv_bfloat16* __restrict__ pages,
                                               const int* __restrict__ table, int key0,
-                                              int first_key, int last_key, int num_kv_heads,
+                                              int first_key, int last_key, int keep_first,
+                                              int num_kv_heads,
                                               int kv_head, int page_size, int page_shift) {
-  // keys outside [first_key, last_key] are zero-filled: their pages may be gone (a window)
-  // or hold anything, and 0 * NaN would poison the sum
-  for (int i = threadIdx.x; i < PF_BN * PF_CHUNKS; i += 128) {
-    const int r = i / PF_CHUNKS, c = i % PF_CHUNKS;
+  // keys outside [first_key, last_key] (and not among the kept first ones) are zero-filled:
+  // their pages may be gone (a window) or hold anything, and 0 * NaN would poison the sum
+  constexpr int CHUNKS = D / 8, STRIDE = D + 8;
+  for (int i = threadIdx.x; i < PF_BN * CHUNKS; i += 128) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
     const int key = key0 + r;
-    const bool valid = key >= first_key && key <= last_key;
+    const bool valid = (key >= first_key || key < keep_first) && key <= last_key;
     const __nv_bfloat16* src = pages;
     if (valid) {
       // a shift and a mask when the page size is a power of two: a division costs more
@@ -88,9 +107,9 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* tile,
       const int index = page_shift >= 0 ? key >> page_shift : key / page_size;
       const int slot = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
       const int page = table[index];
-      src = pages + (((size_t)page * num_kv_heads + kv_head) * page_size + slot) * PF_HD + c * 8;
+      src = pages + (((size_t)page * num_kv_heads + kv_head) * page_size + slot) * D + c * 8;
     }
-    cp_async16(tile + r * PF_STRIDE + c * 8, src, valid);
+    cp_async16(tile + r * STRIDE + c * 8, src, valid);
   }
 }
 
@@ -102,14 +121,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
                          const int* __restrict__ row_start, const int* __restrict__ kv_len,
                          __nv_bfloat16* __restrict__ out, int ld_out, int num_requests,
                          int num_kv_heads, int group, int page_size, float scale, int window,
-                         int total_tiles, int page_shift) {
+                         int total_tiles, int page_shift, int keep_first,
+                         const float* __restrict__ gate, int ld_gate) {
   extern __shared__ __align__(16) unsigned char pf_smem[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(pf_smem);
-  __nv_bfloat16* k_s = q_s + PF_TILE;       // two stages
+  __nv_bfloat16* k_s = q_s + PF_QTILE;      // two stages
   __nv_bfloat16* v_s = k_s + 2 * PF_TILE;   // two stages
 
   pdl_launch_dependents();
-  pdl_wait_for(q, k_pages, v_pages);
+  pdl_wait_for(q, k_pages, v_pages, gate);
   // Which request and which 64-row tile of it. Heads run along grid.x and tiles along grid.y
   // from the last tile down: a tile's work grows with its position in the sequence, and the
   // longest tiles must start first or they finish alone at the end.
@@ -128,8 +148,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   const int length = kv_len[req];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (length == 0) {  // a padding request: zeros
-    for (int i = threadIdx.x; i < nrows * PF_HD; i += 128) {
-      out[(size_t)(first_row + i / PF_HD) * ld_out + head * PF_HD + i % PF_HD] =
+    for (int i = threadIdx.x; i < nrows * PF_VD; i += 128) {
+      out[(size_t)(first_row + i / PF_VD) * ld_out + head * PF_VD + i % PF_VD] =
           __float2bfloat16_rn(0.f);
     }
     return;
@@ -139,6 +159,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   const int lo_min = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int block_lo = lo_min / PF_BN;
   const int block_hi = last_key / PF_BN;  // inclusive
+  // kept first keys that the window of the tile's first row has left behind: their blocks
+  // come first (those that the window's walk does not reach anyway)
+  const int kept = (window > 0 && keep_first < lo_min) ? keep_first : (window > 0 ? lo_min : 0);
+  int kept_blocks = (kept + PF_BN - 1) / PF_BN;
+  if (kept_blocks > block_lo) kept_blocks = block_lo;
+  const int turns = kept_blocks + block_hi - block_lo + 1;
+  const int keep = window > 0 ? keep_first : 0;
   const int* table = block_table + (size_t)req * table_stride;
 
   // Q tile and the first K/V block
@@ -149,28 +176,31 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
         q + (size_t)(first_row + (valid ? r : 0)) * ld_q + head * PF_HD + c * 8;
     cp_async16(q_s + r * PF_STRIDE + c * 8, src, valid);
   }
-  load_kv_block(k_s, k_pages, table, block_lo * PF_BN, lo_min, last_key, num_kv_heads,
-                kv_head, page_size, page_shift);
-  load_kv_block(v_s, v_pages, table, block_lo * PF_BN, lo_min, last_key, num_kv_heads,
-                kv_head, page_size, page_shift);
+  const int block0 = kept_blocks > 0 ? 0 : block_lo;
+  load_kv_block<PF_HD>(k_s, k_pages, table, block0 * PF_BN, lo_min, last_key, keep,
+                       num_kv_heads, kv_head, page_size, page_shift);
+  load_kv_block<PF_VD>(v_s, v_pages, table, block0 * PF_BN, lo_min, last_key, keep,
+                       num_kv_heads, kv_head, page_size, page_shift);
   cp_async_commit();
 
-  float o[PF_HD / 8][4];
+  float o[PF_VD / 8][4];
 #pragma unroll
-  for (int t = 0; t < PF_HD / 8; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f; }
+  for (int t = 0; t < PF_VD / 8; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f; }
   float run_max[2] = {-INFINITY, -INFINITY}, run_sum[2] = {0.f, 0.f};
   const float scale2 = scale * 1.4426950408889634f;  // scores in units of log2
   const int row_a = pos0 + warp * 16 + (lane >> 2);  // position of this thread's first row
   uint32_t q_frag[PF_HD / 16][4];
   bool q_loaded = false;
 
-  for (int block = block_lo; block <= block_hi; ++block) {
-    const int stage = (block - block_lo) & 1;
-    if (block < block_hi) {  // prefetch the next block into the other stage
-      load_kv_block(k_s + (stage ^ 1) * PF_TILE, k_pages, table, (block + 1) * PF_BN, lo_min,
-                    last_key, num_kv_heads, kv_head, page_size, page_shift);
-      load_kv_block(v_s + (stage ^ 1) * PF_TILE, v_pages, table, (block + 1) * PF_BN, lo_min,
-                    last_key, num_kv_heads, kv_head, page_size, page_shift);
+  for (int turn = 0; turn < turns; ++turn) {
+    const int block = turn < kept_blocks ? turn : block_lo + (turn - kept_blocks);
+    const int stage = turn & 1;
+    if (turn + 1 < turns) {  // prefetch the next block into the other stage
+      const int next = turn + 1 < kept_blocks ? turn + 1 : block_lo + (turn + 1 - kept_blocks);
+      load_kv_block<PF_HD>(k_s + (stage ^ 1) * PF_TILE, k_pages, table, next * PF_BN, lo_min,
+                           last_key, keep, num_kv_heads, kv_head, page_size, page_shift);
+      load_kv_block<PF_VD>(v_s + (stage ^ 1) * PF_VTILE, v_pages, table, next * PF_BN, lo_min,
+                           last_key, keep, num_kv_heads, kv_head, page_size, page_shift);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -186,7 +216,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
       q_loaded = true;
     }
     const __nv_bfloat16* kb = k_s + stage * PF_TILE;
-    const __nv_bfloat16* vb = v_s + stage * PF_TILE;
+    const __nv_bfloat16* vb = v_s + stage * PF_VTILE;
 
     // S = Q K^T : 16 rows x 64 keys per warp
     float s[PF_BN / 8][4];
@@ -226,7 +256,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
         for (int e = 0; e < 4; ++e) {
           const int key = key_base + t * 8 + (e & 1);
           const int pos = row_a + (e >> 1) * 8;
-          const bool seen = key <= pos && (window == 0 || key > pos - window);
+          const bool seen = key <= pos && (window == 0 || key > pos - window || key < keep);
           const float v = seen ? s[t][e] * scale2 : -INFINITY;
           s[t][e] = v;
           block_max[e >> 1] = fmaxf(block_max[e >> 1], v);
@@ -257,7 +287,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     run_sum[0] += part[0];
     run_sum[1] += part[1];
 #pragma unroll
-    for (int t = 0; t < PF_HD / 8; ++t) {
+    for (int t = 0; t < PF_VD / 8; ++t) {
       o[t][0] *= corr[0]; o[t][1] *= corr[0];
       o[t][2] *= corr[1]; o[t][3] *= corr[1];
     }
@@ -270,11 +300,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
       pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
       pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-      for (int t = 0; t < PF_HD / 16; ++t) {
+      for (int t = 0; t < PF_VD / 16; ++t) {
         uint32_t vf[4];
         // transposed load: lanes 0-7: keys 16kk..+7 at d chunk 2t; 8-15: keys +8, same chunk;
         // 16-23: keys 16kk..+7 at chunk 2t+1; 24-31: keys +8, chunk 2t+1
-        ldmatrix_x4_trans(vf, vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PF_STRIDE +
+        ldmatrix_x4_trans(vf, vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PF_VSTRIDE +
                                   t * 16 + (lane >> 4) * 8);
         mma_bf16(o[2 * t], pf, vf[0], vf[1]);
         mma_bf16(o[2 * t + 1], pf, vf[2], vf[3]);
@@ -291,19 +321,32 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   }
   const float inv0 = 1.f / run_sum[0], inv1 = 1.f / run_sum[1];
   const int r0 = warp * 16 + (lane >> 2);
+  const float* gate_a = nullptr;  // the raw gates of this thread's two rows
+  const float* gate_b = nullptr;
+  if (gate != nullptr) {
+    if (r0 < nrows) gate_a = gate + (size_t)(first_row + r0) * ld_gate + head * PF_VD;
+    if (r0 + 8 < nrows) gate_b = gate + (size_t)(first_row + r0 + 8) * ld_gate + head * PF_VD;
+  }
 #pragma unroll
-  for (int t = 0; t < PF_HD / 8; ++t) {
+  for (int t = 0; t < PF_VD / 8; ++t) {
     const int col = t * 8 + (lane & 3) * 2;
-    *reinterpret_cast<uint32_t*>(q_s + r0 * PF_STRIDE + col) =
-        pack_bf16(o[t][0] * inv0, o[t][1] * inv0);
-    *reinterpret_cast<uint32_t*>(q_s + (r0 + 8) * PF_STRIDE + col) =
-        pack_bf16(o[t][2] * inv1, o[t][3] * inv1);
+    float a0 = o[t][0] * inv0, a1 = o[t][1] * inv0, b0 = o[t][2] * inv1, b1 = o[t][3] * inv1;
+    if (gate_a != nullptr) {
+      a0 /= 1.f + expf(-gate_a[col]);
+      a1 /= 1.f + expf(-gate_a[col + 1]);
+    }
+    if (gate_b != nullptr) {
+      b0 /= 1.f + expf(-gate_b[col]);
+      b1 /= 1.f + expf(-gate_b[col + 1]);
+    }
+    *reinterpret_cast<uint32_t*>(q_s + r0 * PF_VSTRIDE + col) = pack_bf16(a0, a1);
+    *reinterpret_cast<uint32_t*>(q_s + (r0 + 8) * PF_VSTRIDE + col) = pack_bf16(b0, b1);
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < nrows * PF_CHUNKS; i += 128) {
-    const int r = i / PF_CHUNKS, c = i % PF_CHUNKS;
-    const uint4 v = *reinterpret_cast<const uint4*>(q_s + r * PF_STRIDE + c * 8);
-    *reinterpret_cast<uint4*>(out + (size_t)(first_row + r) * ld_out + head * PF_HD + c * 8) = v;
+  for (int i = threadIdx.x; i < nrows * PF_VCHUNKS; i += 128) {
+    const int r = i / PF_VCHUNKS, c = i % PF_VCHUNKS;
+    const uint4 v = *reinterpret_cast<const uint4*>(q_s + r * PF_VSTRIDE + c * 8);
+    *reinterpret_cast<uint4*>(out + (size_t)(first_row + r) * ld_out + head * PF_VD + c * 8) = v;
   }
 }
 
@@ -313,6 +356,8 @@ AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 AYK_API int ayk_attention_prefill_head_dim() { return ayk::PF_HD; }
 
+AYK_API int ayk_attention_prefill_value_dim() { return ayk::PF_VD; }
+
 // bfloat16 only. q/out rows are 16-byte aligned (ld multiples of 8 elements). `total_tiles`
 // = sum over requests of ceil(rows / 64), computed by the caller from its host copy of the
 // rows.
@@ -321,10 +366,14 @@ AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
                                   const int* row_start, const int* kv_len, void* out, int ld_out,
                                   int num_requests, int total_tiles, int num_heads,
                                   int num_kv_heads, int head_dim, int page_size, float scale,
-                                  int window, void* stream) {
+                                  int window, int value_dim, int keep_first, const float* gate,
+                                  int ld_gate, void* stream) {
   using namespace ayk;
   if (num_requests == 0 || total_tiles == 0) return AYK_OK;
-  if (head_dim != PF_HD) return AYK_BAD_ARGUMENT;
+  if (head_dim != PF_HD || value_dim != PF_VD || keep_first < 0 ||
+      (gate != nullptr && ld_gate < num_heads * PF_VD)) {
+    return AYK_BAD_ARGUMENT;
+  }
   if (num_requests < 0 || total_tiles < 0 || num_heads < 1 || num_kv_heads < 1 ||
       num_heads % num_kv_heads || page_size < 1 || table_stride < 1 || window < 0) {
     return AYK_BAD_ARGUMENT;
@@ -352,5 +401,5 @@ AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
                        table_stride, row_start, kv_len, (__nv_bfloat16*)out, ld_out, num_requests,
                        num_kv_heads, num_heads / num_kv_heads, page_size, scale, window,
-                       total_tiles, page_shift);
+                       total_tiles, page_shift, keep_first, gate, ld_gate);
 }

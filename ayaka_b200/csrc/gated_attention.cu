@@ -17,8 +17,9 @@
 // are walked in a fixed order, first the kept ones that the window has left behind, then the
 // window, in tiles that start at the first visible key: what a row computes depends on its
 // position alone, not on the step's other rows.
-//   generic kernel: one CTA per (row, head) on the CUDA cores, any sizes, both types;
-//   tensor-core kernel (bfloat16): further down.
+// One CTA per (row, head) on the CUDA cores, any sizes, both types: the kernel of single rows
+// and of float32. Prompt portions in bfloat16 run on the tensor cores in
+// attention_prefill.cu, which takes the same mask, value size and gate.
 #include "common.cuh"
 
 namespace ayk {
@@ -68,6 +69,42 @@ gated_prepare_kernel(const float* __restrict__ proj, int ld_proj, int k_off, int
   }
 }
 
+// q . k over one key row, by 16-byte pieces where the row's size allows (rows of the pages
+// then start on 16-byte boundaries).
+__device__ __forceinline__ float dot_row(const float* q, const float* k, int dim) {
+  float sum = 0.f;
+  if (dim % 4 == 0) {
+    for (int d = 0; d < dim; d += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(k + d);
+      sum = fmaf(q[d], v.x, sum);
+      sum = fmaf(q[d + 1], v.y, sum);
+      sum = fmaf(q[d + 2], v.z, sum);
+      sum = fmaf(q[d + 3], v.w, sum);
+    }
+  } else {
+    for (int d = 0; d < dim; ++d) sum = fmaf(q[d], k[d], sum);
+  }
+  return sum;
+}
+__device__ __forceinline__ float dot_row(const float* q, const __nv_bfloat16* k, int dim) {
+  float sum = 0.f;
+  if (dim % 8 == 0) {
+    for (int d = 0; d < dim; d += 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(k + d);
+      const __nv_bfloat162* pair = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(pair[i]);
+        sum = fmaf(q[d + 2 * i], v.x, sum);
+        sum = fmaf(q[d + 2 * i + 1], v.y, sum);
+      }
+    }
+  } else {
+    for (int d = 0; d < dim; ++d) sum = fmaf(q[d], __bfloat162float(k[d]), sum);
+  }
+  return sum;
+}
+
 // One CTA per (row, head). The visible keys, numbered 0 .. total - 1 (kept ones first), are
 // taken GA_THREADS at a time: a thread scores one key, the CTA keeps a running maximum and
 // sum, and thread c sums value entries c, c + GA_THREADS, ...
@@ -111,10 +148,7 @@ gated_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ 
       const long long page = table[at / page_size];
       const long long base = (page * G + kv) * page_size + at % page_size;
       base_s[tid] = base;
-      const T* k = k_pages + base * dim;
-      float sum = 0.f;
-      for (int d = 0; d < dim; ++d) sum = fmaf(qv[d], ldf(k + d), sum);
-      score = sum * scale;
+      score = dot_row(qv, k_pages + base * dim, dim) * scale;
     }
     float best = warp_max(score);
     __syncthreads();

@@ -40,7 +40,7 @@ typedef int (*AttnSimtFn)(const void*, int, const void*, const void*, const int*
                           int, void*);
 typedef int (*AttnPrefillFn)(const void*, int, const void*, const void*, const int*, int,
                              const int*, const int*, void*, int, int, int, int, int, int, int,
-                             float, int, void*);
+                             float, int, int, int, const float*, int, void*);
 typedef int (*AttnPrefillTcFn)(const void*, int, const void*, const void*, const int*, int,
                                const int*, const int*, void*, int, int, int, int, int, int, int,
                                int, float, int, int*, void*);
@@ -311,7 +311,7 @@ int attention_half(const AykAttentionPart* p, AykStep* step, float* residual, vo
           q, ld_qkv, k_pages, v_pages, table, g.table_stride, step->row_start + lead,
           step->kv_len + lead, p->attended, q_width, step->num_requests - lead,
           tiles_of(step, 64, lead), p->num_heads, p->num_kv_heads, p->head_dim, g.page_size,
-          p->scale, p->window, step->stream);
+          p->scale, p->window, p->head_dim, 0, nullptr, 0, step->stream);
     }
   } else {
     if (k.attention_simt == nullptr) return AYK_DRIVER;

@@ -108,7 +108,8 @@ _TIMED = ("embed_rows", "layer_norm", "linear", "linear_kv", "kv_store", "attent
           "latent_prepare", "head_linear", "latent_attention", "latent_decode",
           "causal_conv_silu", "mamba2_scan",
           "mlstm_scan", "gla_scan", "talking_prepare", "talking_attention", "norm_sum",
-          "moe_route", "moe_experts", "moe_join")
+          "moe_route", "moe_experts", "moe_join", "moe_route_scored", "cast_rows", "gated_unit",
+          "norm_add", "gated_attention_prepare", "gated_attention")
 
 
 @contextlib.contextmanager
@@ -127,6 +128,9 @@ def timed() -> Iterator[dict[str, list[tuple[torch.cuda.Event, torch.cuda.Event]
             klass = name
             if name in ("linear", "linear_kv"):
                 klass = f"linear:{args[1].shape[0]}x{args[1].shape[1]}"
+            elif name == "attention_prefill" and (kwargs.get("gate") is not None
+                                                  or kwargs.get("keep_first")):
+                klass = "gated_attention"  # that part's prompt portions run here
             start = torch.cuda.Event(enable_timing=True)
             stop = torch.cuda.Event(enable_timing=True)
             start.record()
@@ -447,13 +451,17 @@ PREFILL_ATTENTION = "tcgen05"
 def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_table: torch.Tensor, row_start: torch.Tensor, kv_len: torch.Tensor,
                       out: torch.Tensor, *, num_heads: int, scale: float, host_rows: list[int],
-                      window: int = 0, kernel: str | None = None) -> None:
+                      window: int = 0, kernel: str | None = None, keep_first: int = 0,
+                      gate: torch.Tensor | None = None) -> None:
     """Causal attention of prompt portions in bfloat16 on the tensor cores.
 
     Request ``b`` owns rows ``row_start[b] .. row_start[b + 1]`` of ``q`` and ``out``, which
     are the last rows of its ``kv_len[b]`` cached tokens; ``host_rows`` is the host copy of
     the row counts (the grid is sized from it). Head size 64 runs on tcgen05; the other head
     sizes on a warp-level kernel compiled for the head size (``kernel`` forces one of them).
+    The warp-level kernel also takes value rows of another size than key rows (``v_pages``'
+    last dimension), ``keep_first`` (with a window: keys before that position stay visible)
+    and ``gate`` (float32 ``[N, num_heads * value size]``: the result times its sigmoid).
     """
     op = "attention_prefill"
     if _left_out and op in _left_out:
@@ -468,20 +476,28 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     if not k_pages.is_contiguous() or not v_pages.is_contiguous():
         raise BackendError(f"{op}: contiguous pages only")
     _, kv_heads, page_size, head_dim = k_pages.shape
+    value_dim = v_pages.shape[3]
     count = len(host_rows)
-    if q.shape[1] != num_heads * head_dim or out.shape[1] != q.shape[1] or \
+    if q.shape[1] != num_heads * head_dim or out.shape[1] != num_heads * value_dim or \
             row_start.shape[0] < count + 1 or kv_len.shape[0] < count or \
-            block_table.shape[0] < count or v_pages.shape != k_pages.shape:
+            block_table.shape[0] < count or v_pages.shape[:3] != k_pages.shape[:3]:
         raise BackendError(f"{op}: shapes do not fit")
-    if head_dim % 16 or not 16 <= head_dim <= 256:
-        raise BackendError(f"{op}: head_dim must be a multiple of 16 in [16, 256]")
+    if head_dim % 16 or not 16 <= head_dim <= 256 or value_dim % 16 or \
+            not 16 <= value_dim <= 256:
+        raise BackendError(f"{op}: head and value sizes must be multiples of 16 in [16, 256]")
+    if gate is not None:
+        _need(op, "gate", gate, torch.float32, 2)
+        if gate.shape[1] != num_heads * value_dim or gate.stride(1) != 1:
+            raise BackendError(f"{op}: the gate does not match the output")
+    plain = value_dim == head_dim and gate is None and not (keep_first and window)
     # the tcgen05 kernel works on tiles of 256 rows: a step of short portions only is better
     # served by the warp-level kernel's tiles of 64
-    which = kernel or (PREFILL_ATTENTION if head_dim == 64 and scale > 0
+    which = kernel or (PREFILL_ATTENTION if head_dim == 64 and scale > 0 and plain
                        and max(host_rows, default=0) >= 256 else "mma")
     if which == "tcgen05":
-        if head_dim != 64:
-            raise BackendError(f"{op}: the tcgen05 kernel serves head size 64, not {head_dim}")
+        if head_dim != 64 or not plain:
+            raise BackendError(f"{op}: the tcgen05 kernel serves head size 64 without a gate, "
+                               f"kept keys or value rows of their own, not {head_dim}")
         lib = library("attention_prefill_tc")
         tile_rows = lib.ayk_attention_prefill_tc_rows()
         tiles = sum(-(-rows // tile_rows) for rows in host_rows)
@@ -494,12 +510,16 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         check(status, op)
         return
     tiles = sum(-(-rows // 64) for rows in host_rows)
-    fn = library("attention_prefill", AYK_HEAD_DIM=head_dim).ayk_attention_prefill
+    sizes = {"AYK_HEAD_DIM": head_dim}
+    if value_dim != head_dim:
+        sizes["AYK_VALUE_DIM"] = value_dim
+    fn = library("attention_prefill", **sizes).ayk_attention_prefill
     status = fn(_ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                 c_int(block_table.stride(0)), _ptr(row_start), _ptr(kv_len), _ptr(out),
                 c_int(out.stride(0)), c_int(count), c_int(tiles), c_int(num_heads),
                 c_int(kv_heads), c_int(head_dim), c_int(page_size), c_float(scale),
-                c_int(window), _stream())
+                c_int(window), c_int(value_dim), c_int(keep_first), _ptr(gate),
+                c_int(0 if gate is None else gate.stride(0)), _stream())
     check(status, op)
 
 

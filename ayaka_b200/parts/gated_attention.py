@@ -7,7 +7,7 @@ import torch
 from ayaka_b200.kernels import ops
 from ayaka_b200.parts.base import BuildContext, CacheNeed, Part, register_part
 from ayaka_b200.parts.context import LayerCache, StepContext
-from ayaka_b200.parts.mixer import Mixer
+from ayaka_b200.parts.mixer import Mixer, leading_single_rows
 from ayaka_b200.parts.spec import PartSpec
 
 __all__ = ["GatedAttention"]
@@ -87,9 +87,24 @@ class GatedAttention(Mixer):
             slot_mapping=group.slot_mapping, k_pages=cache.k_pages if cache.writes else None,
             v_pages=cache.v_pages if cache.writes else None, q=q, heads=self.num_heads,
             kv_heads=self.num_kv_heads, dim=self.head_dim, vdim=self.value_dim, rows=n)
-        ops.gated_attention(
-            q, cache.k_pages, cache.v_pages, group.block_table, step.request_of_row,
-            step.positions, attended, heads=self.num_heads, scale=self.scale,
-            window=self.window, keep_first=self.keep_first,
-            gate=proj[:, self.qkv_width:] if self.gated else None, rows=n)
+        gate = proj[:, self.qkv_width:] if self.gated else None
+        # Prompt portions in bfloat16, where the sizes are the tensor-core kernel's: the
+        # engine's flash kernel, told of the kept keys, the value size and the gate. Single
+        # rows (a decode step, or the decoding requests that lead a mixed step) and every
+        # other size or type go to this part's own kernel.
+        tiled = dtype == torch.bfloat16 and not step.decode_only and \
+            self.head_dim % 16 == 0 and self.value_dim % 16 == 0 and \
+            max(self.head_dim, self.value_dim) <= 256
+        lead = (leading_single_rows(step.host_rows) if tiled else n)
+        if lead:
+            ops.gated_attention(
+                q, cache.k_pages, cache.v_pages, group.block_table, step.request_of_row,
+                step.positions, attended, heads=self.num_heads, scale=self.scale,
+                window=self.window, keep_first=self.keep_first, gate=gate, rows=lead)
+        if tiled:
+            ops.attention_prefill(
+                q, cache.k_pages, cache.v_pages, group.block_table[lead:],
+                step.row_start[lead:], step.kv_len[lead:], attended, num_heads=self.num_heads,
+                scale=self.scale, host_rows=step.host_rows[lead:], window=self.window,
+                keep_first=self.keep_first, gate=gate)
         ops.linear(attended, self.out_weight, None, out, residual=accumulate, rows=n)

@@ -1,7 +1,8 @@
-"""``bench.py --design mapuvik`` / ``--design gagotar``: prefill and decode throughput of the
-design at sizes that resemble a real model's layers, beside GPT-2 of the same width, heads,
+"""``bench.py --design mapuvik`` / ``gagotar`` / ``semadra``: prefill and decode throughput of
+the design at sizes that resemble a real model's layers, beside GPT-2 of the same width, heads,
 feed-forward and number of layers (Gagotar also beside Mapuvik, the design whose kernels are
-closest to its own), on one B200 with random bf16 weights.
+closest to its own; Semadra beside Gagotar, whose experts and attention, and Mapuvik, whose
+latent attention are the like kernels), on one B200 with random bf16 weights.
 
 For each size and model: one prompt step of 2,048 tokens (two prompts of 1,024) and one decode
 step of 8 requests at context 1,025, each timed on the device as a CUDA-graph replay of the
@@ -61,6 +62,36 @@ def gagotar_config(width: int, heads: int, ff: int, layers: int, vocab: int) -> 
     entry = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp}
     return {"architecture": "Gagotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "layers": [entry for _ in range(layers)]}
+
+
+#: Semadra at the bench's sizes: windows of 512 positions (a prompt of 1,024 passes over
+#: them, the decode step at context 1,025 sees 512 keys, the gated attention 64 kept ones
+#: more); latents of 256 entries (a row size the engine's own attention kernels take); a dense
+#: first layer, then experts as in Gagotar's configuration with a shared one beside them
+SEMADRA_WINDOW, SEMADRA_KEEP, SEMADRA_EXPERTS, SEMADRA_TOP = 512, 64, 16, 2
+
+
+def semadra_config(width: int, heads: int, ff: int, repeats: int, vocab: int) -> dict:
+    head = width // heads
+    latent = {"heads": heads, "dim": head, "vdim": head, "kv_rank": 256, "q_rank": width // 2,
+              "scale": head ** -0.5, "mask": {"size": SEMADRA_WINDOW}}
+    attention = {"heads": heads, "kv_heads": heads // 4, "dim": head, "vdim": head,
+                 "scale": head ** -0.5,
+                 "mask": {"size": SEMADRA_WINDOW, "keep_first": SEMADRA_KEEP}}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
+           "router": {"experts": SEMADRA_EXPERTS, "top": SEMADRA_TOP, "scale": 2.5,
+                      "groups": {"count": 4, "keep": 2}}}
+    layers = []
+    for repeat in range(repeats):
+        at = 3 * repeat
+        layers += [
+            {"type": "latent_attention", "mixer": dict(latent),
+             "mlp": moe if repeat else {"kind": "dense", "ff": ff}},
+            {"type": "latent_attention", "mixer": {**latent, "kv_from": at}, "mlp": moe},
+            {"type": "attention", "mixer": attention, "mlp": moe}]
+    return {"architecture": "Semadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": width ** 0.5}, "residual_mult": 0.5,
+            "token_side": {"dim": 64}, "layers": layers}
 
 
 def gpt2_config(width: int, heads: int, ff: int, layers: int, vocab: int) -> dict:
@@ -156,6 +187,70 @@ def _class_work(config: dict, rows: int, keys_per_row: float, decode: bool,
             add("moe_experts", 2.0 * rows * top * 3 * f * width,
                 min(E, rows * top) * 3 * f * width * 2 + rows * top * (width * 6 + f * 4))
             add("moe_join", 0.0, rows * width * (4 * top + 8))
+        product(config["vocab"], width, 4, wanted)
+        return work
+    if config["architecture"] == "Semadra":
+        side = (config.get("token_side") or {}).get("dim", 0)
+        add("cast_rows", 0.0, rows * width * 6)
+
+        def gated(inner: int) -> None:  # act(gate) * up between two products
+            product(2 * inner, width, 4)
+            add("gated_unit", 0.0, rows * inner * 10)
+            product(width, inner, 4)
+
+        for layer in config["layers"]:
+            m, mlp = layer["mixer"], layer["mlp"]
+            H, dim, vdim = m["heads"], m["dim"], m["vdim"]
+            window = (m.get("mask") or {}).get("size", 0)
+            keep = (m.get("mask") or {}).get("keep_first", 0)
+
+            def seen(p: int) -> int:  # keys the row at position p attends
+                if not window or p < window:
+                    return p + 1
+                return window + min(keep, p + 1 - window)
+
+            keys = seen(int(keys_per_row) - 1) if decode else \
+                sum(seen(p) for p in range(LENGTH)) / LENGTH
+            reuse = 1 if decode else 64 / 8  # a tile of 64 rows shares its keys
+            if layer["type"] == "attention":
+                G = m.get("kv_heads", H)
+                product(H * dim + G * (dim + vdim) + H * vdim, width, 4)
+                add("gated_attention_prepare", 0.0,
+                    rows * (H * dim + G * (dim + vdim)) * 6)
+                add("gated_attention", 2.0 * rows * keys * H * (dim + vdim),
+                    rows * keys * G * (dim + vdim) * 2 / reuse + rows * H * (dim + 5 * vdim))
+            else:
+                rank, q_rank = m["kv_rank"], m["q_rank"]
+                own = 0 if "kv_from" in m else rank
+                product(q_rank + own, width, 4)
+                add("rms_norm", 0.0, rows * q_rank * 6)
+                product(H * dim, q_rank, 4)
+                add("latent_prepare", 0.0, rows * (H * dim * 6 + own * 6))
+                add("head_linear", 2.0 * rows * H * rank * (dim + vdim),
+                    H * rank * (dim + vdim) * 2 + rows * H * (dim + vdim + 2 * rank) * 2)
+                add("latent_attention", 4.0 * rows * keys * H * rank,
+                    rows * keys * rank * 2 / reuse)
+            product(width, H * vdim, 4)
+            add("norm_add", 0.0, rows * width * 14)
+            if mlp is not None:
+                if mlp["kind"] == "dense":
+                    gated(mlp["ff"])
+                else:
+                    E, top, f = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+                    product(E, width, 4)
+                    add("moe_route_scored", 0.0, rows * (E + 2 * top) * 4)
+                    add("moe_experts", 2.0 * rows * top * 3 * f * width,
+                        min(E, rows * top) * 3 * f * width * 2 + rows * top * (width * 6 + f * 4))
+                    add("moe_join", 0.0, rows * width * (4 * top + 8))
+                    if mlp.get("shared"):
+                        gated(mlp["shared"]["ff"])
+                add("norm_add", 0.0, rows * width * 14)
+            if side:
+                product(side, width, 4)
+                add("gated_unit", 0.0, rows * side * 8)
+                product(width, side, 4)
+                add("norm_add", 0.0, rows * width * 14)
+        add("rms_norm", 0.0, wanted * width * 6)
         product(config["vocab"], width, 4, wanted)
         return work
     for layer in config["layers"]:
@@ -275,6 +370,8 @@ def _measure(config: dict, peak: dict) -> dict:
                 name = klass
                 if klass == "attention_prefill":
                     name = "latent_attention" if "latent_attention" in work else "attention"
+                elif klass == "latent_decode":
+                    name = "latent_attention"
                 if name in work:
                     us = sum(start.elapsed_time(stop) for start, stop in pairs) * 1000
                     found.setdefault(name, {"us": 0.0})["us"] += us
@@ -339,13 +436,18 @@ def run(sizes: str | None = None, design: str = "mapuvik") -> dict:
     for name in picked:
         width, heads, ff, repeats = table[name]
         results[name] = {"layers": 3 * repeats, "width": width, "heads": heads, "ff": ff}
-        if design == "gagotar":
+        if design == "semadra":
+            results[name]["semadra"] = _measure(
+                semadra_config(width, heads, ff, repeats, 32000), peak)
+        if design in ("gagotar", "semadra"):
             results[name]["gagotar"] = _measure(
                 gagotar_config(width, heads, ff, 3 * repeats, 32000), peak)
         results[name]["mapuvik"] = _measure(mapuvik_config(width, heads, ff, repeats, 32000),
                                             peak)
         results[name]["gpt2"] = _measure(gpt2_config(width, heads, ff, 3 * repeats, 32000), peak)
-    title = "Gagotar beside Mapuvik and GPT-2" if design == "gagotar" else "Mapuvik beside GPT-2"
+    title = {"gagotar": "Gagotar beside Mapuvik and GPT-2",
+             "semadra": "Semadra beside Gagotar, Mapuvik and GPT-2"}.get(
+                 design, "Mapuvik beside GPT-2")
     return {"metric": f"{title} of equal size: one 2,048-token prompt step and one "
                       "decode step of 8 requests at context 1,025 (bf16, random weights)",
             "peaks": {**{k: peak[k] for k in ("hbm_gbs", "bf16_tflops")}, "source": source},

@@ -211,6 +211,75 @@ def test_gated_attention_sees_its_window_and_the_kept_tokens_and_not_a_key_more(
             close(got[i, h], want, tol, f"request {b} position {p} head {h}")
 
 
+TILED_CASES = [
+    # heads, kv heads, dim, vdim, window, keep_first, page
+    (6, 3, 32, 16, 40, 24, 16),
+    (2, 1, 64, 64, 70, 5, 32),
+    (4, 2, 48, 80, 130, 70, 16),   # kept keys beyond one tile of keys
+    (2, 2, 16, 32, 64, 64, 8),     # the window and the kept stretch end on a tile's edge
+    (3, 1, 128, 16, 0, 9, 16),     # no window: nothing is kept apart
+    (2, 1, 32, 32, 5, 200, 16),    # everything is kept
+]
+
+
+@pytest.mark.parametrize("gated", [True, False])
+@pytest.mark.parametrize("case", TILED_CASES)
+def test_the_tiled_kernel_takes_the_kept_tokens_a_value_size_and_a_gate(case, gated):
+    """Prompt portions of several lengths (one row to more than four tiles of rows) on the
+    tensor-core kernel. For the last row of every request the last kept key, the oldest key
+    of the window and, louder, the key just before the window are made to stand out."""
+    heads, groups, dim, vdim, window, keep, page = case
+    lengths = [1, 2, 17, 65, 150, 333, 400]
+    tails = [1, 2, 17, 3, 150, 70, 270]
+    per, dtype = heads // groups, torch.bfloat16
+    direction = randn(dim, seed=9)
+    direction = direction / direction.norm()
+    keys = [randn(t, groups, dim, seed=20 + i, scale=0.3) for i, t in enumerate(lengths)]
+    values = [randn(t, groups, vdim, seed=40 + i) for i, t in enumerate(lengths)]
+    queries, request_of_row, positions, row_start = [], [], [], [0]
+    for b, (t, tail) in enumerate(zip(lengths, tails)):
+        for p in range(t - tail, t):
+            queries.append(randn(heads, dim, seed=1000 * b + p, scale=0.5) + 3.0 * direction)
+            request_of_row.append(b)
+            positions.append(p)
+        row_start.append(len(positions))
+        p = t - 1
+        oldest = max(0, p - window + 1) if window else 0
+        keys[b][oldest] += 5.0 * direction
+        if oldest > keep:
+            keys[b][oldest - 1] += 10.0 * direction
+        if keep and oldest > keep:
+            keys[b][keep - 1] += 5.0 * direction
+    keys = [k.to(dtype).double() for k in keys]
+    values = [v.to(dtype).double() for v in values]
+    q = torch.stack(queries).to(dtype)
+    need = sum(-(-t // page) for t in lengths)
+    order = (torch.randperm(need, generator=gen(4)) + 1).tolist()
+    k_pages, table = _paged(keys, page, dtype, order, need + 1)
+    v_pages, _ = _paged(values, page, dtype, order, need + 1)
+    n, scale = len(positions), 0.8
+    gate = randn(n, heads * vdim, seed=78, scale=2.0).float()
+    out = torch.full((n + 1, heads * vdim), 7.0, dtype=dtype, device=DEV)
+    ops.attention_prefill(q.reshape(n, heads * dim).to(DEV), k_pages, v_pages, table,
+                          torch.tensor(row_start, dtype=torch.int32, device=DEV),
+                          torch.tensor(lengths, dtype=torch.int32, device=DEV), out,
+                          num_heads=heads, scale=scale, host_rows=tails, window=window,
+                          keep_first=keep, gate=gate.to(DEV) if gated else None)
+    got = out[:n].double().cpu().reshape(n, heads, vdim)
+    assert torch.isfinite(got).all() and float((out[n] - 7.0).abs().max()) == 0.0
+    for i, (b, p) in enumerate(zip(request_of_row, positions)):
+        if i % 3 and p != lengths[b] - 1 and p % 64 not in (0, 63):
+            continue  # every third row, the tiles' edges and the rows with the loud keys
+        mask = plain.visible(p + 1, window or p + 1, keep if window else 0)[p]
+        for h in range(heads):
+            scores = scale * (keys[b][:p + 1, h // per] @ q[i, h].double())
+            weights = torch.softmax(scores.masked_fill(~mask, -math.inf), dim=-1)
+            want = weights @ values[b][:p + 1, h // per]
+            if gated:
+                want = want * torch.sigmoid(gate[i].double().reshape(heads, vdim)[h])
+            close(got[i, h], want, 1.5e-2, f"request {b} position {p} head {h}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_prepare_norms_the_whole_projections_and_stores_where_the_slots_say(dtype):
     heads, groups, dim, vdim, page, rows, eps = 4, 2, 12, 20, 8, 10, 1e-3
