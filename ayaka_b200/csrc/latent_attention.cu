@@ -13,6 +13,8 @@
 // kernels of this file; the projections before and after are the engine's matrix products.
 //
 // All arithmetic in fp32; T is the type of the cache, of the queries and of the outputs.
+#include <type_traits>
+
 #include "rope.cuh"
 
 namespace ayk {
@@ -97,21 +99,22 @@ __global__ void latent_prepare_kernel(const float* __restrict__ proj, int ld_pro
 // at a time.
 constexpr int HL_BN = 64;
 
-// A CTA of 256 threads computes (256 / (HL_BN / TN)) * TM rows x HL_BN columns, BK of the
-// inner dimension at a time: <2, 4, 16> is 32 rows x 64 columns for prompt portions; <1, 2, 64>
-// is 8 rows x 64 columns in a quarter of the turns, for the few rows of a decode step, where
-// what counts is the number of trips to memory, not the arithmetic.
-template <typename T, int TM, int TN, int BK>
+// A CTA of 256 threads computes (256 / (BN / TN)) * TM rows x BN columns, BK of the inner
+// dimension at a time: <2, 4, 16> is 32 rows x 64 columns for prompt portions; <1, 1, 64, 16>
+// is 16 rows x 16 columns in a quarter of the turns, for the few rows of a decode step, where
+// what counts is the number of trips to memory and of CTAs that make them at once (a head's
+// 64 columns over four CTAs), not the arithmetic.
+template <typename T, int TM, int TN, int BK, int BN = HL_BN>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const T* __restrict__ a, int ld_a, int a_head, const T* __restrict__ w,
                    long long w_head, int w_in, int w_out, const float* __restrict__ gate,
                    int ld_gate, T* __restrict__ out, int ld_out, int out_head, int rows, int I,
                    int J) {
-  constexpr int TX = HL_BN / TN, TY = 256 / TX, BM = TY * TM;
+  constexpr int TX = BN / TN, TY = 256 / TX, BM = TY * TM;
   __shared__ float a_s[BK][BM + 1];
-  __shared__ float w_s[BK][HL_BN + 1];
+  __shared__ float w_s[BK][BN + 1];
   pdl_launch_dependents();
-  const int h = blockIdx.z, m0 = blockIdx.x * BM, n0 = blockIdx.y * HL_BN;
+  const int h = blockIdx.z, m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
   const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
   const T* wh = w + (size_t)h * w_head;
   pdl_wait_for(a, gate);
@@ -123,11 +126,11 @@ head_linear_kernel(const T* __restrict__ a, int ld_a, int a_head, const T* __res
       const int m = m0 + mm, k = k0 + kk;
       a_s[kk][mm] = (m < rows && k < I) ? ldf(ah + (size_t)m * ld_a + k) : 0.f;
     }
-    for (int idx = threadIdx.x; idx < BK * HL_BN; idx += 256) {
+    for (int idx = threadIdx.x; idx < BK * BN; idx += 256) {
       int kk, nn;
       if (w_out == 1) {  // consecutive threads along the unit stride
-        nn = idx % HL_BN;
-        kk = idx / HL_BN;
+        nn = idx % BN;
+        kk = idx / BN;
       } else {
         kk = idx % BK;
         nn = idx / BK;
@@ -168,14 +171,174 @@ head_linear_kernel(const T* __restrict__ a, int ld_a, int a_head, const T* __res
   }
 }
 
+// ---- the same product for bfloat16 prompt portions, on the warp-level tensor cores -----------
+// (warp-level fragments; also used by the decode kernel further down)
+__device__ __forceinline__ void lm_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void lm_ldmatrix_x4_trans(uint32_t* r, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void lm_ldmatrix_x4(uint32_t* r, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ void lm_cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;  // (0: the 16 bytes are zero-filled, nothing is read)
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes)
+               : "memory");
+}
+
+// A CTA of four warps computes 64 rows x 64 columns of one head, 64 of the inner dimension at
+// a time through two stages of asynchronous 16-byte copies (zero fill past the edges); a warp
+// owns 16 rows. K_ROWS: W_h is stored [j][i] (i contiguous: the B operand's own layout);
+// otherwise [i][j] (j contiguous: fragments by transposing loads). fp32 accumulators summed
+// in the order of i whatever the batch; the gate and the one rounding in the epilogue.
+// Sizes: I, J, ld_a, a_head, ld_w and w_head multiples of 8, ld_out and out_head even.
+constexpr int HM_TILE = 64, HM_STRIDE = HM_TILE + 8;
+
+template <bool K_ROWS>
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const __nv_bfloat16* __restrict__ a, int ld_a, int a_head,
+                       const __nv_bfloat16* __restrict__ w, long long w_head, int ld_w,
+                       const float* __restrict__ gate, int ld_gate,
+                       __nv_bfloat16* __restrict__ out, int ld_out, int out_head, int rows,
+                       int I, int J) {
+  __shared__ __align__(16) __nv_bfloat16 a_s[2][HM_TILE * HM_STRIDE];
+  __shared__ __align__(16) __nv_bfloat16 w_s[2][HM_TILE * HM_STRIDE];
+  pdl_launch_dependents();
+  const int h = blockIdx.z, m0 = blockIdx.x * HM_TILE, n0 = blockIdx.y * HM_TILE;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* wh = w + (size_t)h * w_head;
+  pdl_wait_for(a, gate);
+  const __nv_bfloat16* ah = a + (size_t)h * a_head;
+
+  auto load = [&](int stage, int k0) {
+    for (int idx = threadIdx.x; idx < HM_TILE * 8; idx += 128) {
+      const int r = idx >> 3, c = (idx & 7) * 8;
+      const bool valid = m0 + r < rows && k0 + c < I;
+      lm_cp_async16(&a_s[stage][r * HM_STRIDE + c],
+                    valid ? ah + (size_t)(m0 + r) * ld_a + k0 + c : ah, valid);
+      if (K_ROWS) {  // row r of the tile is column n0 + r of the result
+        const bool ok = n0 + r < J && k0 + c < I;
+        lm_cp_async16(&w_s[stage][r * HM_STRIDE + c],
+                      ok ? wh + (size_t)(n0 + r) * ld_w + k0 + c : wh, ok);
+      } else {       // row r of the tile is inner index k0 + r
+        const bool ok = k0 + r < I && n0 + c < J;
+        lm_cp_async16(&w_s[stage][r * HM_STRIDE + c],
+                      ok ? wh + (size_t)(k0 + r) * ld_w + n0 + c : wh, ok);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float acc[HM_TILE / 8][4];
+#pragma unroll
+  for (int t = 0; t < HM_TILE / 8; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+  const int turns = (I + HM_TILE - 1) / HM_TILE;
+  load(0, 0);
+  for (int turn = 0; turn < turns; ++turn) {
+    const int stage = turn & 1;
+    if (turn + 1 < turns) {
+      load(stage ^ 1, (turn + 1) * HM_TILE);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const __nv_bfloat16* at = a_s[stage];
+    const __nv_bfloat16* wt = w_s[stage];
+#pragma unroll
+    for (int kk = 0; kk < HM_TILE / 16; ++kk) {
+      uint32_t af[4];
+      lm_ldmatrix_x4(af, at + (warp * 16 + (lane & 15)) * HM_STRIDE + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int t = 0; t < HM_TILE / 16; ++t) {
+        uint32_t bf[4];
+        if (K_ROWS) {
+          // lanes 0-7: columns 16t..+7, inner piece 0; 8-15: the same columns, piece 1;
+          // 16-23: columns +8, piece 0; 24-31: columns +8, piece 1
+          lm_ldmatrix_x4(bf, wt + (t * 16 + (lane & 7) + ((lane >> 4) << 3)) * HM_STRIDE +
+                                 kk * 16 + ((lane >> 3) & 1) * 8);
+        } else {
+          // transposed: lanes 0-7: inner 16kk..+7 at column piece 2t; 8-15: inner +8, the same
+          // piece; 16-23: inner 16kk..+7 at piece 2t + 1; 24-31: inner +8, piece 2t + 1
+          lm_ldmatrix_x4_trans(bf, wt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) *
+                                            HM_STRIDE + t * 16 + (lane >> 4) * 8);
+        }
+        lm_mma(acc[2 * t], af, bf[0], bf[1]);
+        lm_mma(acc[2 * t + 1], af, bf[2], bf[3]);
+      }
+    }
+    __syncthreads();  // the stage is filled again at the next turn
+  }
+  const int r0 = m0 + warp * 16 + (lane >> 2);
+#pragma unroll
+  for (int t = 0; t < HM_TILE / 8; ++t) {
+    const int n = n0 + t * 8 + (lane & 3) * 2;
+    if (n >= J) continue;  // (J is even: n + 1 < J too)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = r0 + half * 8;
+      if (m >= rows) continue;
+      float v0 = acc[t][2 * half], v1 = acc[t][2 * half + 1];
+      if (gate != nullptr) {
+        const float* z = gate + (size_t)m * ld_gate + (size_t)h * J + n;
+        v0 *= 1.f / (1.f + expf(-z[0]));
+        v1 *= 1.f / (1.f + expf(-z[1]));
+      }
+      *reinterpret_cast<uint32_t*>(out + (size_t)m * ld_out + (size_t)h * out_head + n) =
+          lm_pack(v0, v1);
+    }
+  }
+}
+
+inline bool head_linear_mma_takes(const void* a, int ld_a, int a_head, const void* w,
+                                  long long w_head, int ld_w, const void* out, int ld_out,
+                                  int out_head, int rows, int I, int J) {
+  return rows > 16 && I % 8 == 0 && J % 8 == 0 && ld_a % 8 == 0 && a_head % 8 == 0 &&
+         ld_w % 8 == 0 && w_head % 8 == 0 && ld_out % 2 == 0 && out_head % 2 == 0 &&
+         ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 3) == 0;
+}
+
 template <typename T>
 int head_linear(const void* a, int ld_a, int a_head, const void* w, long long w_head, int w_in,
                 int w_out, const float* gate, int ld_gate, void* out, int ld_out, int out_head,
                 int rows, int heads, int I, int J, cudaStream_t s) {
   const int tiles = (J + HL_BN - 1) / HL_BN;
   if (tiles > 65535) return AYK_TOO_LARGE;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const int ld_w = w_in == 1 ? w_out : w_in;
+    if (head_linear_mma_takes(a, ld_a, a_head, w, w_head, ld_w, out, ld_out, out_head, rows, I,
+                              J)) {
+      const dim3 grid((rows + HM_TILE - 1) / HM_TILE, tiles, heads);
+      if (w_in == 1) {
+        return launch_kernel(head_linear_mma_kernel<true>, grid, dim3(128), 0, s, 1,
+                             (const T*)a, ld_a, a_head, (const T*)w, w_head, ld_w, gate,
+                             ld_gate, (T*)out, ld_out, out_head, rows, I, J);
+      }
+      return launch_kernel(head_linear_mma_kernel<false>, grid, dim3(128), 0, s, 1,
+                           (const T*)a, ld_a, a_head, (const T*)w, w_head, ld_w, gate, ld_gate,
+                           (T*)out, ld_out, out_head, rows, I, J);
+    }
+  }
   if (rows <= 16) {
-    return launch_kernel(head_linear_kernel<T, 1, 2, 64>, dim3((rows + 7) / 8, tiles, heads),
+    return launch_kernel(head_linear_kernel<T, 1, 1, 64, 16>, dim3(1, (J + 15) / 16, heads),
                          dim3(256), 0, s, 1, (const T*)a, ld_a, a_head, (const T*)w, w_head,
                          w_in, w_out, gate, ld_gate, (T*)out, ld_out, out_head, rows, I, J);
   }
@@ -496,24 +659,6 @@ constexpr int LM_WARPS = 4;
 inline int& decode_tensor_cores() {
   static int enabled = 1;
   return enabled;
-}
-
-__device__ __forceinline__ void lm_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
-      "{%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void lm_ldmatrix_x4_trans(uint32_t* r, const void* p) {
-  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(a));
-}
-__device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 template <int NT16>  // the accumulator holds NT16 stretches of 16 entries: rank <= 16 * NT16

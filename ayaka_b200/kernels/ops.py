@@ -30,6 +30,8 @@ __all__ = [
     "embed_rows",
     "gated_attention",
     "gated_attention_prepare",
+    "gated_decode",
+    "gated_decode_shares",
     "gated_unit",
     "head_linear",
     "kv_store",
@@ -109,7 +111,7 @@ _TIMED = ("embed_rows", "layer_norm", "linear", "linear_kv", "kv_store", "attent
           "causal_conv_silu", "mamba2_scan",
           "mlstm_scan", "gla_scan", "talking_prepare", "talking_attention", "norm_sum",
           "moe_route", "moe_experts", "moe_join", "moe_route_scored", "cast_rows", "gated_unit",
-          "norm_add", "gated_attention_prepare", "gated_attention")
+          "norm_add", "gated_attention_prepare", "gated_attention", "gated_decode")
 
 
 @contextlib.contextmanager
@@ -128,9 +130,9 @@ def timed() -> Iterator[dict[str, list[tuple[torch.cuda.Event, torch.cuda.Event]
             klass = name
             if name in ("linear", "linear_kv"):
                 klass = f"linear:{args[1].shape[0]}x{args[1].shape[1]}"
-            elif name == "attention_prefill" and (kwargs.get("gate") is not None
-                                                  or kwargs.get("keep_first")):
-                klass = "gated_attention"  # that part's prompt portions run here
+            elif name == "gated_decode" or name == "attention_prefill" and (
+                    kwargs.get("gate") is not None or kwargs.get("keep_first")):
+                klass = "gated_attention"  # that part's single rows and prompt portions
             start = torch.cuda.Event(enable_timing=True)
             stop = torch.cuda.Event(enable_timing=True)
             start.record()
@@ -1668,3 +1670,69 @@ def gated_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         c_float(scale), c_int(window), c_int(keep_first), c_int(1 if tensor_cores else 0),
         c_int(_TYPE[q.dtype]), _stream())
     check(status, op)
+
+
+def gated_decode_shares(rows: int, heads: int, reach: int,
+                        device: torch.device | None = None) -> int:
+    """Shares a row's visible keys are cut into by :func:`gated_decode`: down to one tile of
+    128 keys a share while that gives no more than eight CTAs per SM over all rows and heads;
+    at most 32."""
+    want = -(-8 * sm_count(device) // max(1, rows * heads))
+    return max(1, min(want, -(-reach // 128), 32))
+
+
+def gated_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                 block_table: torch.Tensor, request_of_row: torch.Tensor,
+                 positions: torch.Tensor, out: torch.Tensor, partial: torch.Tensor | None, *,
+                 heads: int, scale: float, window: int = 0, keep_first: int = 0,
+                 gate: torch.Tensor | None = None, rows: int, shares: int) -> bool:
+    """:func:`gated_attention` for steps of single rows: a row's visible keys are cut into
+    ``shares`` shares, one CTA each per head, and joined in their order. ``partial`` is
+    float32 scratch of at least ``rows * heads * shares * (vdim + 2)`` elements (``None`` with
+    one share). Returns False, having run nothing, for sizes the kernel does not take (value
+    rows that are not whole 16-byte pieces)."""
+    op = "gated_decode"
+    if _left_out and ("gated_attention" in _left_out or op in _left_out):
+        return True
+    _need(op, "q", q, ndim=2)
+    _need(op, "out", out, q.dtype, 2)
+    _need(op, "k_pages", k_pages, q.dtype, 4)
+    _need(op, "v_pages", v_pages, q.dtype, 4)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "request_of_row", request_of_row, torch.int32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    if q.dtype not in _TYPE or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise BackendError(f"{op}: contiguous float32 or bfloat16 pages only")
+    _, kv_heads, page_size, dim = k_pages.shape
+    vdim = v_pages.shape[3]
+    if q.shape[1] != heads * dim or out.shape[1] != heads * vdim or \
+            tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3]) or rows > out.shape[0] or \
+            rows > q.shape[0] or rows > request_of_row.shape[0] or \
+            rows > positions.shape[0] or heads % kv_heads or shares < 1:
+        raise BackendError(f"{op}: shapes do not fit")
+    if shares > 1:
+        if partial is None:
+            raise BackendError(f"{op}: more than one share needs scratch")
+        _need(op, "partial", partial, torch.float32)
+        if not partial.is_contiguous() or \
+                partial.numel() < rows * heads * shares * (vdim + 2):
+            raise BackendError(f"{op}: the scratch is too small")
+    if gate is not None:
+        _need(op, "gate", gate, torch.float32, 2)
+        if gate.shape[1] != heads * vdim or gate.shape[0] < rows or gate.stride(1) != 1:
+            raise BackendError(f"{op}: the gate does not match the rows")
+    global _launches
+    status = library("gated_attention").ayk_gated_decode(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+        c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions), _ptr(gate),
+        c_int(0 if gate is None else gate.stride(0)), _ptr(partial if shares > 1 else None),
+        _ptr(out), c_int(out.stride(0)), c_int(rows), c_int(heads), c_int(kv_heads),
+        c_int(dim), c_int(vdim), c_int(page_size), c_float(scale), c_int(window),
+        c_int(keep_first), c_int(shares), c_int(_TYPE[q.dtype]), _stream())
+    if status == -6:  # AYK_NOT_TAKEN
+        _launches -= 1
+        return False
+    if shares > 1:
+        _launches += 1  # the merge of the shares is a launch of its own
+    check(status, op)
+    return True

@@ -96,11 +96,28 @@ class GatedAttention(Mixer):
             self.head_dim % 16 == 0 and self.value_dim % 16 == 0 and \
             max(self.head_dim, self.value_dim) <= 256
         lead = (leading_single_rows(step.host_rows) if tiled else n)
+        taken = 0
+        if lead and (step.decode_only or tiled):
+            # single rows: a row's keys in shares, a CTA per head and share
+            reach = step.max_kv_len
+            if self.window:
+                reach = min(reach, self.window + self.keep_first)
+            shares = ops.gated_decode_shares(lead, self.num_heads, reach, hidden.device)
+            partial = None if shares == 1 else work.buffer(
+                "gated_attention.partial", self.num_heads * (self.value_dim + 2),
+                torch.float32, rows=n * shares)
+            if ops.gated_decode(
+                    q, cache.k_pages, cache.v_pages, group.block_table, step.request_of_row,
+                    step.positions, attended, partial, heads=self.num_heads, scale=self.scale,
+                    window=self.window, keep_first=self.keep_first, gate=gate, rows=lead,
+                    shares=shares):
+                lead, taken = 0, lead
         if lead:
             ops.gated_attention(
                 q, cache.k_pages, cache.v_pages, group.block_table, step.request_of_row,
                 step.positions, attended, heads=self.num_heads, scale=self.scale,
                 window=self.window, keep_first=self.keep_first, gate=gate, rows=lead)
+        lead = lead or taken
         if tiled:
             ops.attention_prefill(
                 q, cache.k_pages, cache.v_pages, group.block_table[lead:],

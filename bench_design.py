@@ -381,8 +381,9 @@ def _measure(config: dict, peak: dict) -> dict:
             seconds = max(entry["us"], 1e-3) * 1e-6
             by_flops = work[name]["flops"] / seconds / tflops
             by_bytes = work[name]["bytes"] / seconds / gbs
-            tensor = not decode and (name.startswith("linear") or "attention" in name
-                                     or name in ("head_linear", "moe_experts"))
+            tensor = not decode and "prepare" not in name and (
+                name.startswith("linear") or "attention" in name
+                or name in ("head_linear", "moe_experts"))
             entry["frac"] = round(by_flops if tensor else by_bytes, 4)
             entry["of"] = "bf16_tflops" if tensor else "hbm_gbs"
         return found

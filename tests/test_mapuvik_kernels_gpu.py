@@ -109,6 +109,37 @@ def test_head_linear_both_orientations_and_the_gate(dtype, rows, heads, inner, o
     close(tight.reshape(rows, heads, outer), want, tol, "transposed with gate")
 
 
+@pytest.mark.parametrize("rows, heads, inner, outer", [(17, 2, 8, 8), (64, 3, 64, 72),
+                                                       (200, 5, 136, 64), (65, 1, 72, 256)])
+def test_head_linear_of_prompt_portions_on_the_tensor_cores(rows, heads, inner, outer):
+    """bfloat16, more than 16 rows, sizes in 16-byte pieces: both orientations, heads of ``a``
+    and of the result wider than what is used (their padding untouched), the gate, row and
+    column counts that end inside a tile, an inner size of more than one turn."""
+    dtype, pad = torch.bfloat16, 8
+    a = randn(rows, heads, inner + pad, seed=15).to(dtype)
+    a[..., inner:] = float("nan")  # (never read)
+    stored = randn(heads * outer, inner, seed=16).to(dtype)       # [out, in] per head
+    across = randn(heads * inner, outer, seed=17).to(dtype)       # [in, out] per head
+    gate = randn(rows, heads * outer, seed=18)
+    a64 = a.double()[..., :inner]
+    flat = a.reshape(rows, heads * (inner + pad)).to(DEV)
+    out = torch.full((rows + 1, heads * (outer + pad)), 3.0, dtype=dtype, device=DEV)
+    ops.head_linear(flat, across.to(DEV), out, heads=heads, transposed=True, rows=rows,
+                    inner=inner)
+    want = torch.einsum("nhi,hij->nhj", a64, across.double().reshape(heads, inner, outer))
+    got = out[:rows].reshape(rows, heads, outer + pad)
+    close(got[..., :outer], want, 1e-2, "as stored")
+    assert float((got[..., outer:] - 3.0).abs().max()) == 0.0
+    assert float((out[rows] - 3.0).abs().max()) == 0.0
+    tight = torch.full((rows + 1, heads * outer), 3.0, dtype=dtype, device=DEV)
+    ops.head_linear(flat, stored.to(DEV), tight, heads=heads, transposed=False, rows=rows,
+                    gate=gate.float().to(DEV), inner=inner)
+    want = torch.einsum("nhi,hji->nhj", a64, stored.double().reshape(heads, outer, inner))
+    want = want * torch.sigmoid(gate.float().double()).reshape(rows, heads, outer)
+    close(tight[:rows].reshape(rows, heads, outer), want, 1e-2, "transposed with gate")
+    assert float((tight[rows] - 3.0).abs().max()) == 0.0
+
+
 # ---- attention over latent rows ---------------------------------------------------------------
 def _paged(rows_of_request: list[torch.Tensor], page: int, dtype, shuffle_seed: int):
     """Scatter each request's rows [T, D] over pages handed out in a shuffled order."""

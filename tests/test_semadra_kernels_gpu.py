@@ -154,15 +154,20 @@ CASES = [
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("case", CASES)
-@pytest.mark.parametrize("rows_kind", ["ends", "portions"])
+@pytest.mark.parametrize("rows_kind, shares", [("ends", 0), ("portions", 0), ("ends", 1),
+                                               ("ends", 3), ("portions", 16)])
 def test_gated_attention_sees_its_window_and_the_kept_tokens_and_not_a_key_more(
-        dtype, case, rows_kind):
+        dtype, case, rows_kind, shares):
     """Three keys are made to stand out for every query asked: the last kept one, the oldest
     one in its window, and, louder than both, the one just before the window that is not
     kept. The first two share nearly all the weight, the third gets none. ``ends``: single
     rows at the ends of sequences (a decode step); ``portions``: the last rows of every
-    sequence together (prompt portions, beside single rows)."""
+    sequence together (prompt portions, beside single rows). ``shares`` > 0: the kernel of
+    single rows, which cuts a row's visible keys into that many shares (more shares than
+    some rows have keys), with a row of padding at the end."""
     heads, groups, dim, vdim, window, keep, page = case
+    if shares and vdim % (4 if dtype == torch.float32 else 8):
+        pytest.skip("value rows that are no whole 16-byte pieces go to the other kernel")
     lengths = [1, 2, page, page + 1, 3 * page - 1, 150, 333]
     per = heads // groups
     direction = randn(dim, seed=9)
@@ -193,11 +198,26 @@ def test_gated_attention_sees_its_window_and_the_kept_tokens_and_not_a_key_more(
     n, scale = len(positions), 0.8
     gate = randn(n, heads * vdim, seed=77, scale=2.0).float()
     out = torch.full((n + 1, heads * vdim), 7.0, dtype=dtype, device=DEV)
-    ops.gated_attention(q.reshape(n, heads * dim).to(DEV), k_pages, v_pages, table,
-                        torch.tensor(request_of_row, dtype=torch.int32, device=DEV),
-                        torch.tensor(positions, dtype=torch.int32, device=DEV), out,
-                        heads=heads, scale=scale, window=window, keep_first=keep,
-                        gate=gate.to(DEV), rows=n)
+    if shares:
+        partial = torch.full(((n + 1) * heads * shares * (vdim + 2),), float("nan"),
+                             device=DEV)
+        out = torch.full((n + 2, heads * vdim), 7.0, dtype=dtype, device=DEV)
+        assert ops.gated_decode(
+            torch.cat([q.reshape(n, heads * dim), q.reshape(n, heads * dim)[:1]]).to(DEV),
+            k_pages, v_pages, table,
+            torch.tensor(request_of_row + [-1], dtype=torch.int32, device=DEV),
+            torch.tensor(positions + [0], dtype=torch.int32, device=DEV), out, partial,
+            heads=heads, scale=scale, window=window, keep_first=keep,
+            gate=torch.cat([gate, gate[:1]]).to(DEV), rows=n + 1, shares=shares)
+        assert float(out[n].float().abs().max()) == 0.0  # the row of padding
+        assert float((out[n + 1] - 7.0).abs().max()) == 0.0
+        out = torch.cat([out[:n], out[n + 1:]])
+    else:
+        ops.gated_attention(q.reshape(n, heads * dim).to(DEV), k_pages, v_pages, table,
+                            torch.tensor(request_of_row, dtype=torch.int32, device=DEV),
+                            torch.tensor(positions, dtype=torch.int32, device=DEV), out,
+                            heads=heads, scale=scale, window=window, keep_first=keep,
+                            gate=gate.to(DEV), rows=n)
     got = out[:n].double().cpu().reshape(n, heads, vdim)
     assert torch.isfinite(got).all() and float((out[n] - 7.0).abs().max()) == 0.0
     tol = 2e-5 if dtype == torch.float32 else 1.5e-2
