@@ -101,7 +101,8 @@ constexpr int HL_BN = 64;
 
 // A CTA of 256 threads computes (256 / (BN / TN)) * TM rows x BN columns, BK of the inner
 // dimension at a time: <2, 4, 16> is 32 rows x 64 columns for prompt portions; <1, 1, 64, 16>
-// is 16 rows x 16 columns in a quarter of the turns, for the few rows of a decode step, where
+// (<1, 1, 256, 16> for a longer inner dimension) is 16 rows x 16 columns in a quarter (a
+// sixteenth) of the turns, for the few rows of a decode step, where
 // what counts is the number of trips to memory and of CTAs that make them at once (a head's
 // 64 columns over four CTAs), not the arithmetic.
 template <typename T, int TM, int TN, int BK, int BN = HL_BN>
@@ -139,8 +140,9 @@ head_linear_kernel(const T* __restrict__ a, int ld_a, int a_head, const T* __res
       w_s[kk][nn] = (n < J && k < I) ? ldf(wh + (size_t)k * w_in + (size_t)n * w_out) : 0.f;
     }
     __syncthreads();
-#pragma unroll
-    for (int kk = 0; kk < BK; ++kk) {
+    const int kmax = min(BK, I - k0);  // (what lies beyond holds zeros)
+#pragma unroll 16
+    for (int kk = 0; kk < kmax; ++kk) {
       float av[TM];
 #pragma unroll
       for (int r = 0; r < TM; ++r) av[r] = a_s[kk][ty * TM + r];
@@ -338,6 +340,11 @@ int head_linear(const void* a, int ld_a, int a_head, const void* w, long long w_
     }
   }
   if (rows <= 16) {
+    if (I > 64) {  // up to 256 of the inner dimension in one trip to memory
+      return launch_kernel(head_linear_kernel<T, 1, 1, 256, 16>, dim3(1, (J + 15) / 16, heads),
+                           dim3(256), 0, s, 1, (const T*)a, ld_a, a_head, (const T*)w, w_head,
+                           w_in, w_out, gate, ld_gate, (T*)out, ld_out, out_head, rows, I, J);
+    }
     return launch_kernel(head_linear_kernel<T, 1, 1, 64, 16>, dim3(1, (J + 15) / 16, heads),
                          dim3(256), 0, s, 1, (const T*)a, ld_a, a_head, (const T*)w, w_head,
                          w_in, w_out, gate, ld_gate, (T*)out, ld_out, out_head, rows, I, J);
