@@ -166,6 +166,41 @@ __global__ void norm_add_kernel(const float* __restrict__ x, int ld_x,
   __shared__ float scratch[33];
   pdl_launch_dependents();
   const int r = blockIdx.x;
+  // A row of up to NA_KEEP entries a thread stays in registers: the weights are fetched before
+  // the kernel ahead has finished, the branch and the stream's row in one trip to memory, and
+  // nothing is read twice. The sums run in the same order as in the loops below.
+  constexpr int NA_KEEP = 8;
+  if (width <= NA_KEEP * (int)blockDim.x) {
+    float ws[NA_KEEP], xs[NA_KEEP], ds[NA_KEEP];
+#pragma unroll
+    for (int i = 0; i < NA_KEEP; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      ws[i] = c < width ? offset + weight[c] : 0.f;
+    }
+    pdl_wait_for(x, dst);
+    const float* src = x + (size_t)r * ld_x;
+    float* to = dst + (size_t)r * ld_dst;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NA_KEEP; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      xs[i] = c < width ? src[c] : 0.f;
+      ds[i] = c < width ? to[c] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < NA_KEEP; ++i) s += xs[i] * xs[i];
+    const float inv = factor / sqrtf(block_sum(s, scratch) / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < NA_KEEP; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < width) {
+        const float v = ds[i] + xs[i] * inv * ws[i];
+        to[c] = v;
+        if (copy != nullptr) stf(copy + (size_t)r * ld_copy + c, v);
+      }
+    }
+    return;
+  }
   pdl_wait_for(x, dst);
   const float* src = x + (size_t)r * ld_x;
   float s = 0.f;
