@@ -113,6 +113,7 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* tile,
   }
 }
 
+template <bool SAME>  // the value pages are the key pages: one tile serves both products
 __global__ void __launch_bounds__(128)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
                          const __nv_bfloat16* __restrict__ k_pages,
@@ -126,7 +127,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   extern __shared__ __align__(16) unsigned char pf_smem[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(pf_smem);
   __nv_bfloat16* k_s = q_s + PF_QTILE;      // two stages
-  __nv_bfloat16* v_s = k_s + 2 * PF_TILE;   // two stages
+  // keys that are their own values (attention over latent rows passes the same pages twice):
+  // one tile serves both products, half the copies and room for a second CTA on the SM
+  constexpr bool same = SAME;
+  __nv_bfloat16* v_s = same ? k_s : k_s + 2 * PF_TILE;  // two stages
 
   pdl_launch_dependents();
   pdl_wait_for(q, k_pages, v_pages, gate);
@@ -179,8 +183,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   const int block0 = kept_blocks > 0 ? 0 : block_lo;
   load_kv_block<PF_HD>(k_s, k_pages, table, block0 * PF_BN, lo_min, last_key, keep,
                        num_kv_heads, kv_head, page_size, page_shift);
-  load_kv_block<PF_VD>(v_s, v_pages, table, block0 * PF_BN, lo_min, last_key, keep,
-                       num_kv_heads, kv_head, page_size, page_shift);
+  if (!same) {
+    load_kv_block<PF_VD>(v_s, v_pages, table, block0 * PF_BN, lo_min, last_key, keep,
+                         num_kv_heads, kv_head, page_size, page_shift);
+  }
   cp_async_commit();
 
   float o[PF_VD / 8][4];
@@ -199,8 +205,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
       const int next = turn + 1 < kept_blocks ? turn + 1 : block_lo + (turn + 1 - kept_blocks);
       load_kv_block<PF_HD>(k_s + (stage ^ 1) * PF_TILE, k_pages, table, next * PF_BN, lo_min,
                            last_key, keep, num_kv_heads, kv_head, page_size, page_shift);
-      load_kv_block<PF_VD>(v_s + (stage ^ 1) * PF_VTILE, v_pages, table, next * PF_BN, lo_min,
-                           last_key, keep, num_kv_heads, kv_head, page_size, page_shift);
+      if (!same) {
+        load_kv_block<PF_VD>(v_s + (stage ^ 1) * PF_VTILE, v_pages, table, next * PF_BN, lo_min,
+                             last_key, keep, num_kv_heads, kv_head, page_size, page_shift);
+      }
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -384,9 +392,15 @@ AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
   }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          PF_SMEM_BYTES);
+    if constexpr (PF_VD == PF_HD) {
+      if (e == cudaSuccess) {
+        e = cudaFuncSetAttribute(attention_prefill_kernel<true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES);
+      }
+    }
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -396,7 +410,18 @@ AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
     page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
   }
-  return launch_kernel(attention_prefill_kernel, dim3(num_heads, total_tiles), dim3(128),
+  if constexpr (PF_VD == PF_HD) {
+    if (v_pages == k_pages) {  // (attention over latent rows)
+      return launch_kernel(attention_prefill_kernel<true>, dim3(num_heads, total_tiles),
+                           dim3(128), (PF_QTILE + 2 * PF_TILE) * 2, (cudaStream_t)stream, 1,
+                           (const __nv_bfloat16*)q, ld_q, (const __nv_bfloat16*)k_pages,
+                           (const __nv_bfloat16*)v_pages, block_table, table_stride, row_start,
+                           kv_len, (__nv_bfloat16*)out, ld_out, num_requests, num_kv_heads,
+                           num_heads / num_kv_heads, page_size, scale, window, total_tiles,
+                           page_shift, keep_first, gate, ld_gate);
+    }
+  }
+  return launch_kernel(attention_prefill_kernel<false>, dim3(num_heads, total_tiles), dim3(128),
                        PF_SMEM_BYTES, (cudaStream_t)stream, 1, (const __nv_bfloat16*)q, ld_q,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
                        table_stride, row_start, kv_len, (__nv_bfloat16*)out, ld_out, num_requests,

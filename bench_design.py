@@ -362,7 +362,7 @@ def _measure(config: dict, peak: dict) -> dict:
             filler = torch.empty(64 << 20, device="cuda")
             for _ in range(2):
                 with ops.timed() as record:
-                    for _ in range(20):
+                    for _ in range(60):  # (a step of 300 launches takes the host 3 ms)
                         filler.zero_()  # the device is busy while the host queues the step
                     body()
                 torch.cuda.synchronize()
