@@ -18,6 +18,8 @@
 // (with a window: keys j < keep_first stay visible to every later row; the blocks that hold
 // them are walked first, then the window's, so the walk still depends on positions alone) and
 // `gate` (fp32, one raw gate per output entry: the result is multiplied by its sigmoid).
+// When the value pages are the key pages themselves (attention over latent rows) the kernel's
+// other instantiation fetches one tile per block of keys and uses it in both products.
 //
 // This kernel uses the legacy warp-level tensor path (not tcgen05): attention is ~5% of a
 // prefill step's FLOPs and this dataflow is proven; the matrix products that dominate run on
