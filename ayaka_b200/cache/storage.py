@@ -44,7 +44,8 @@ class CachePlan:
     def bytes_per_page(self, group: int, itemsize: int, page_size: int) -> int:
         need = self.groups[group]
         entries = need.head_dim + (need.value_head_dim if need.values else 0)
-        return self.slots_per_group[group] * need.num_kv_heads * page_size * entries * itemsize
+        rows = page_size + (-(-page_size // need.pool) if need.pool else 0)
+        return self.slots_per_group[group] * need.num_kv_heads * rows * entries * itemsize
 
     def bytes_per_token(self, itemsize: int) -> int:
         """Key and value bytes one cached token takes over all groups (windows ignored)."""
@@ -53,8 +54,8 @@ class CachePlan:
 
 def _same_rows(a: CacheNeed, b: CacheNeed) -> bool:
     """Whether two needs lay a token's rows out alike (how far back they look aside)."""
-    return (a.num_kv_heads, a.head_dim, a.values, a.value_head_dim) == \
-        (b.num_kv_heads, b.head_dim, b.values, b.value_head_dim)
+    return (a.num_kv_heads, a.head_dim, a.values, a.value_head_dim, a.pool) == \
+        (b.num_kv_heads, b.head_dim, b.values, b.value_head_dim, b.pool)
 
 
 def _covering(a: CacheNeed, b: CacheNeed) -> CacheNeed:
@@ -66,7 +67,7 @@ def _covering(a: CacheNeed, b: CacheNeed) -> CacheNeed:
     chunk = a.chunk if a.chunk == b.chunk and not (a.window or b.window) else 0
     keep_first = max(a.keep_first, b.keep_first) if window else 0
     return CacheNeed(a.num_kv_heads, a.head_dim, window, a.values, chunk, a.value_dim,
-                     keep_first)
+                     keep_first, a.pool)
 
 
 def plan_cache(order: tuple[Run, ...],
@@ -127,12 +128,23 @@ class CacheStorage:
         self.page_size = page_size
         self.keys: list[torch.Tensor] = []
         self.values: list[torch.Tensor | None] = []
+        #: per group, the rows of pooled blocks beside the pages (keys, values) or ``None``
+        self.pooled: list[tuple[torch.Tensor, torch.Tensor] | None] = []
         for need, slots, pages in zip(plan.groups, plan.slots_per_group, num_pages):
             shape = (slots, pages, need.num_kv_heads, page_size, need.head_dim)
             self.keys.append(torch.zeros(shape, dtype=dtype, device=device))
             # a group of latent rows keeps one tensor: its rows are keys and values at once
             self.values.append(torch.zeros((*shape[:-1], need.value_head_dim), dtype=dtype,
                                            device=device) if need.values else None)
+            if need.pool and need.values:
+                rows = -(-page_size // need.pool)
+                self.pooled.append((
+                    torch.zeros((slots, pages, need.num_kv_heads, rows, need.head_dim),
+                                dtype=dtype, device=device),
+                    torch.zeros((slots, pages, need.num_kv_heads, rows, need.value_head_dim),
+                                dtype=dtype, device=device)))
+            else:
+                self.pooled.append(None)
         if poison:
             self.poison()
         self.states: list[torch.Tensor | None] = [
@@ -142,7 +154,8 @@ class CacheStorage:
 
     def poison(self) -> None:
         """Fill every page with NaN (tests: a slot read before it is written then shows)."""
-        for tensor in (*self.keys, *self.values):
+        pooled = [t for pair in self.pooled if pair is not None for t in pair]
+        for tensor in (*self.keys, *self.values, *pooled):
             if tensor is not None:
                 tensor.fill_(float("nan"))
 
@@ -155,9 +168,12 @@ class CacheStorage:
             else:
                 slot = self.plan.run_slot[index]
                 values = self.values[group]
+                pooled = self.pooled[group]
                 out.append(LayerCache(group, self.keys[group][slot],
                                       None if values is None else values[slot],
-                                      self.plan.run_writes[index], self.states[index]))
+                                      self.plan.run_writes[index], self.states[index],
+                                      None if pooled is None else pooled[0][slot],
+                                      None if pooled is None else pooled[1][slot]))
         return out
 
     def zero_state_rows(self, rows: list[int]) -> None:
@@ -168,6 +184,7 @@ class CacheStorage:
                 state[rows] = 0
 
     def nbytes(self) -> int:
-        total = sum(t.numel() * t.element_size() for t in (*self.keys, *self.values)
+        pooled = [t for pair in self.pooled if pair is not None for t in pair]
+        total = sum(t.numel() * t.element_size() for t in (*self.keys, *self.values, *pooled)
                     if t is not None)
         return total + sum(t.numel() * t.element_size() for t in self.states if t is not None)

@@ -4,7 +4,10 @@
 //   unit:  out[r][c] = act(gate[r][c]) * other[r][c], act = silu or the tanh GELU, where
 //          `other` is either a second fp32 matrix (the up half of a gated feed-forward) or a
 //          row of a table picked by an index per row, from column `col` on (an embedding of
-//          the row's token that gates a projection of the residual stream).
+//          the row's token that gates a projection of the residual stream);
+//   unary: out[r][c] = act(x[r][c] + bias[c]), act = tanh, or a quadratic-exponential unit
+//          with two learned numbers (p, q): for z > 0, softplus(p) z^2 + z / 2; for z <= 0,
+//          (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2.
 #include "common.cuh"
 
 namespace ayk {
@@ -47,6 +50,40 @@ __global__ void gated_unit_kernel(const float* __restrict__ gate, int ld_gate,
       if (t >= 0 && t < table_rows) b = ldf(table + (size_t)t * ld_table + col + c);
     }
     stf(out + (size_t)r * ld_out + c, a * b);
+  }
+}
+
+enum UnaryAct : int { UNARY_TANH = 0, UNARY_XIELU = 1 };
+
+__device__ __forceinline__ float softplus_of(float z) {  // log(1 + e^z), exact for any z
+  return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+}
+
+template <typename T>
+__global__ void unary_rows_kernel(const float* __restrict__ x, int ld_x,
+                                  const float* __restrict__ bias, int act,
+                                  const float* __restrict__ numbers, T* __restrict__ out,
+                                  int ld_out, int rows, int width) {
+  pdl_launch_dependents();
+  float up = 0.f, down = 0.f;
+  if (act == UNARY_XIELU) {  // (parameters: written once, when the model was loaded)
+    up = softplus_of(numbers[0]);
+    down = 0.5f + softplus_of(numbers[1]);
+  }
+  pdl_wait_for(x);
+  const long long total = (long long)rows * width;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / width), c = (int)(i % width);
+    float z = x[(size_t)r * ld_x + c];
+    if (bias != nullptr) z += bias[c];
+    float y;
+    if (act == UNARY_TANH) {
+      y = tanhf(z);
+    } else {
+      y = z > 0.f ? fmaf(up * z, z, 0.5f * z) : fmaf(down, expm1f(z) - z, 0.5f * z);
+    }
+    stf(out + (size_t)r * ld_out + c, y);
   }
 }
 
@@ -109,6 +146,31 @@ AYK_API int ayk_gated_unit(const float* gate, int ld_gate, const float* other, i
                          dim3(threads), 0, s, 1, gate, ld_gate, other, ld_other,
                          (const __nv_bfloat16*)table, ld_table, index, table_rows, col, act,
                          (__nv_bfloat16*)out, ld_out, rows, width);
+  }
+  return AYK_BAD_ARGUMENT;
+}
+
+// act: 0 = tanh, 1 = the quadratic-exponential unit with `numbers` = (p, q). `bias` may be
+// null. out_type: 0 = float32, 1 = bfloat16.
+AYK_API int ayk_unary_rows(const float* x, int ld_x, const float* bias, int act,
+                           const float* numbers, void* out, int ld_out, int rows, int width,
+                           int out_type, void* stream) {
+  using namespace ayk;
+  if (rows == 0) return AYK_OK;
+  if (rows < 0 || width < 1 || x == nullptr || out == nullptr || ld_x < width ||
+      ld_out < width || (act != UNARY_TANH && act != UNARY_XIELU) ||
+      (act == UNARY_XIELU && numbers == nullptr)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  const int threads = 256, blocks = blocks_for((long long)rows * width, threads);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (out_type == 0) {
+    return launch_kernel(unary_rows_kernel<float>, dim3(blocks), dim3(threads), 0, s, 1, x, ld_x,
+                         bias, act, numbers, (float*)out, ld_out, rows, width);
+  }
+  if (out_type == 1) {
+    return launch_kernel(unary_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, 1,
+                         x, ld_x, bias, act, numbers, (__nv_bfloat16*)out, ld_out, rows, width);
   }
   return AYK_BAD_ARGUMENT;
 }

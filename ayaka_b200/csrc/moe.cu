@@ -3,7 +3,8 @@
 // A step's rows each choose `top` of E experts. A (row, choice) is a *pair*; pair p = row *
 // top + choice. Four launches, none of which needs the host to know a count:
 //   route:   per row, the `top` largest router logits (fp32; ties to the smaller index) and
-//            the softmax over just those -> chosen[p], share[p];
+//            the softmax over just those (or, `over_all`, their part of the softmax over
+//            every expert) -> chosen[p], share[p];
 //   align:   pairs grouped by expert into a list whose every expert's stretch is padded to
 //            a multiple of the tile's rows (-1 = no pair), and the expert of every tile;
 //   experts: two grouped products over those tiles. The first computes, per pair,
@@ -13,7 +14,8 @@
 //   join:    dst[row] (+)= scale * sum_choice share * (W_down y)[pair], choices in order.
 // A pair's result does not depend on its place in a tile or on the other pairs: every output
 // element is one sum over k in a fixed order. Experts' matrices lie one under the other:
-// w_in [E][2 * ff][width] (an expert's gate rows, then its up rows), w_out [E][width][ff].
+// w_in [E][2 * ff][width] (an expert's gate rows, then its up rows), w_out [E][width][ff]. An
+// expert without a gate (`single`: y = relu(W_up h)^2) has w_in [E][ff][width].
 //
 // The tile products run on the CUDA cores with fp32 FMA for float32 and on the warp-level
 // tensor cores (mma.sync m16n8k16, fp32 accumulators) for bfloat16.
@@ -32,7 +34,8 @@ constexpr int MOE_MAX_EXPERTS = 1024;
 // ---------------------------------------------------------------------------------------------
 // One warp per row. Lane l holds logits l, l + 32, ...; `top` times the largest not yet taken.
 __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, int rows, int E,
-                                 int top, int* __restrict__ chosen, float* __restrict__ share) {
+                                 int top, int over_all, int* __restrict__ chosen,
+                                 float* __restrict__ share) {
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -70,6 +73,11 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, int r
       chosen[(size_t)row * top + j] = at;
       share[(size_t)row * top + j] = e;
     }
+  }
+  if (over_all) {  // the softmax's sum runs over every expert: the shares are not renormalised
+    float all = 0.f;
+    for (int e = lane; e < E; e += 32) all += expf(z[e] - first);
+    total = warp_sum(all);
   }
   __syncwarp();
   if (lane < top) share[(size_t)row * top + lane] /= total;
@@ -208,7 +216,12 @@ moe_align_kernel(const int* __restrict__ chosen, int pairs, int E, int max_tiles
 // top), the weight tile is rows n0.. of the expert's gate part and of its up part, the result
 // y[place][n] in the compute type. PHASE 1: rows of `a` are y[place], the weight tile rows
 // n0.. of the expert's down matrix, the result out[pair][n] in fp32.
-__device__ __forceinline__ float expert_unit(float g, float u, float limit, float alpha, float shift) {
+__device__ __forceinline__ float expert_unit(float g, float u, float limit, float alpha, float shift,
+                                             int single) {
+  if (single) {  // one matrix, the square of relu
+    g = fmaxf(g, 0.f);
+    return g * g;
+  }
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
   return g / (1.f + expf(-alpha * g)) * (u + shift);
@@ -229,7 +242,8 @@ template <int PHASE> struct TileAcc<float, PHASE, MOE_TM> {
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[w][i][j] = 0.f;
   }
-  __device__ __forceinline__ void step(const float* As, const float* Bs, const float* Bs2) {
+  __device__ __forceinline__ void step(const float* As, const float* Bs, const float* Bs2,
+                                       bool both) {
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
 #pragma unroll
     for (int k = 0; k < MOE_TK; ++k) {
@@ -242,7 +256,7 @@ template <int PHASE> struct TileAcc<float, PHASE, MOE_TM> {
       for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[0][i][j] = fmaf(av[i], bv[j], acc[0][i][j]);
-      if (PHASE == 0) {
+      if (PHASE == 0 && both) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) bv[j] = Bs2[(tx * 4 + j) * LDS + k];
 #pragma unroll
@@ -304,7 +318,7 @@ template <int PHASE, int TM> struct TileAcc<__nv_bfloat16, PHASE, TM> {
                  : "r"(address));
   }
   __device__ __forceinline__ void step(const __nv_bfloat16* As, const __nv_bfloat16* Bs,
-                                       const __nv_bfloat16* Bs2) {
+                                       const __nv_bfloat16* Bs2, bool both) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = (warp / WARPS_N) * 16 * MT, n0 = (warp % WARPS_N) * 8 * NT;
     // A: lanes 0-15 give rows 0-15 at k, lanes 16-31 the same rows at k + 8 (a0..a3);
@@ -325,7 +339,7 @@ template <int PHASE, int TM> struct TileAcc<__nv_bfloat16, PHASE, TM> {
           mma(acc[0][m][n], a[m], b[0], b[1]);
           mma(acc[0][m][n + 1], a[m], b[2], b[3]);
         }
-        if (PHASE == 0) {
+        if (PHASE == 0 && both) {
           load_tiles(b, Bs2 + b_offset + n * 8 * LDS + k0);
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
@@ -357,7 +371,7 @@ __global__ void __launch_bounds__(256, 2)  // two CTAs an SM: one's copies under
 moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
                 const int* __restrict__ sorted, const int* __restrict__ tile_expert, int top,
                 int K, int N, float limit, float alpha, float shift, T* __restrict__ y, int ld_y,
-                float* __restrict__ out, int ld_out, int wide) {
+                float* __restrict__ out, int ld_out, int wide, int single) {
   using Acc = TileAcc<T, PHASE, TM>;
   constexpr int LDS = Acc::LDS, TK = Acc::TK;
   constexpr bool BF16 = sizeof(T) == 2;
@@ -373,7 +387,9 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
   if (tid < TM) pair_s[tid] = sorted[tile * TM + tid];
   __syncthreads();
   // an expert's matrices: PHASE 0 [2 N][K] (gate rows, then up rows), PHASE 1 [N][K]
-  const T* w = weight + (size_t)e * (PHASE == 0 ? 2 : 1) * N * K;
+  // (`single`: an expert without a gate, PHASE 0 [N][K] too)
+  const bool both = PHASE == 0 && !single;
+  const T* w = weight + (size_t)e * (both ? 2 : 1) * N * K;
   Acc acc;
   acc.zero();
   if (BF16 && wide) {
@@ -404,7 +420,7 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
         const int r = n0 + pr + 32 * i;
         const bool in = in_k && r < N;
         rb[i] = in ? *reinterpret_cast<const uint4*>(w + (size_t)r * K + k0 + pk) : zero;
-        if (PHASE == 0) {
+        if (both) {
           rb2[i] = in ? *reinterpret_cast<const uint4*>(w + (size_t)(N + r) * K + k0 + pk) : zero;
         }
       }
@@ -418,11 +434,11 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         *reinterpret_cast<uint4*>(Bs + (pr + 32 * i) * LDS + pk) = rb[i];
-        if (PHASE == 0) *reinterpret_cast<uint4*>(Bs2 + (pr + 32 * i) * LDS + pk) = rb2[i];
+        if (both) *reinterpret_cast<uint4*>(Bs2 + (pr + 32 * i) * LDS + pk) = rb2[i];
       }
       __syncthreads();
       if (k0 + TK < K) fetch(k0 + TK);
-      acc.step(As, Bs, Bs2);
+      acc.step(As, Bs, Bs2, both);
       __syncthreads();
     }
   } else {
@@ -441,10 +457,10 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
         const int r = idx / TK, k = idx % TK;
         const bool in = n0 + r < N && k0 + k < K;
         Bs[r * LDS + k] = in ? w[(size_t)(n0 + r) * K + k0 + k] : T(0.f);
-        if (PHASE == 0) Bs2[r * LDS + k] = in ? w[(size_t)(N + n0 + r) * K + k0 + k] : T(0.f);
+        if (both) Bs2[r * LDS + k] = in ? w[(size_t)(N + n0 + r) * K + k0 + k] : T(0.f);
       }
       __syncthreads();
-      acc.step(As, Bs, Bs2);
+      acc.step(As, Bs, Bs2, both);
       __syncthreads();
     }
   }
@@ -453,7 +469,7 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
     if (pair < 0 || n0 + c >= N) return;
     if (PHASE == 0) {
       stf(y + ((size_t)tile * TM + r) * ld_y + n0 + c,
-          expert_unit(first, second, limit, alpha, shift));
+          expert_unit(first, second, limit, alpha, shift, single));
     } else {
       out[(size_t)pair * ld_out + n0 + c] = first;
     }
@@ -482,8 +498,8 @@ __global__ void moe_join_kernel(const float* __restrict__ pair_out, int ld, cons
 template <typename T, int TM>
 int moe_experts(const void* hidden, int ld_hidden, const void* w_in, const void* w_out,
                 const int* sorted, const int* tile_expert, int max_tiles, int top, int width,
-                int ff, float limit, float alpha, float shift, void* y, int ld_y, float* pair_out, int ld_out,
-                cudaStream_t stream) {
+                int ff, float limit, float alpha, float shift, int single, void* y, int ld_y,
+                float* pair_out, int ld_out, cudaStream_t stream) {
   // 16-byte pieces when every row of every operand starts on a 16-byte boundary
   const auto aligned = [](const void* p) { return ((uintptr_t)p % 16) == 0; };
   const int wide_in = sizeof(T) == 2 && width % 8 == 0 && ld_hidden % 8 == 0 &&
@@ -503,12 +519,12 @@ int moe_experts(const void* hidden, int ld_hidden, const void* w_in, const void*
   int status = launch_kernel(moe_tile_kernel<T, 0, TM>, grid_in, dim3(256), 0, stream, 1,
                              (const T*)hidden, ld_hidden, (const T*)w_in, sorted, tile_expert,
                              top, width, ff, limit, alpha, shift, (T*)y, ld_y, (float*)nullptr, 0,
-                             wide_in);
+                             wide_in, single);
   if (status != AYK_OK) return status;
   const dim3 grid_out(max_tiles, (width + MOE_TN - 1) / MOE_TN);
   return launch_kernel(moe_tile_kernel<T, 1, TM>, grid_out, dim3(256), 0, stream, 1, (const T*)y,
                        ld_y, (const T*)w_out, sorted, tile_expert, top, ff, width, limit, alpha, shift,
-                       (T*)nullptr, 0, pair_out, ld_out, wide_out);
+                       (T*)nullptr, 0, pair_out, ld_out, wide_out, 0);
 }
 
 }  // namespace ayk
@@ -519,7 +535,7 @@ AYK_API int ayk_moe_tile_rows() { return ayk::MOE_TM; }
 AYK_API int ayk_moe_tile_rows_wide() { return ayk::MOE_TM_WIDE; }
 
 AYK_API int ayk_moe_route(const float* logits, int ld, int rows, int experts, int top,
-                          int* chosen, float* share, void* stream) {
+                          int over_all, int* chosen, float* share, void* stream) {
   using namespace ayk;
   if (rows == 0) return AYK_OK;
   if (rows < 0 || experts < 1 || top < 1 || top > experts || ld < experts ||
@@ -529,7 +545,8 @@ AYK_API int ayk_moe_route(const float* logits, int ld, int rows, int experts, in
   if (experts > MOE_MAX_EXPERTS) return AYK_TOO_LARGE;
   const int warps = 4;
   return launch_kernel(moe_route_kernel, dim3((rows + warps - 1) / warps), dim3(32 * warps), 0,
-                       (cudaStream_t)stream, 1, logits, ld, rows, experts, top, chosen, share);
+                       (cudaStream_t)stream, 1, logits, ld, rows, experts, top, over_all, chosen,
+                       share);
 }
 
 // Scores instead of a softmax: see moe_route_scored_kernel. `groups` divides `experts`,
@@ -558,7 +575,8 @@ AYK_API int ayk_moe_route_scored(const float* logits, int ld, int rows, int expe
 // of width. type: 0 = float32, 1 = bfloat16. tile_rows: 32, or 128 (bfloat16 only).
 AYK_API int ayk_moe_experts(const void* hidden, int ld_hidden, const void* w_in,
                             const void* w_out, const int* chosen, int rows, int experts, int top,
-                            int width, int ff, float limit, float alpha, float shift, int* sorted,
+                            int width, int ff, float limit, float alpha, float shift, int single,
+                            int* sorted,
                             int* tile_expert, int max_tiles, int tile_rows, void* y, int ld_y,
                             float* pair_out, int ld_out, int type, void* stream) {
   using namespace ayk;
@@ -580,17 +598,18 @@ AYK_API int ayk_moe_experts(const void* hidden, int ld_hidden, const void* w_in,
   if (status != AYK_OK) return status;
   if (type == 0) {
     return moe_experts<float, MOE_TM>(hidden, ld_hidden, w_in, w_out, sorted, tile_expert, max_tiles,
-                              top, width, ff, limit, alpha, shift, y, ld_y, pair_out, ld_out, s);
+                              top, width, ff, limit, alpha, shift, single, y, ld_y, pair_out,
+                              ld_out, s);
   }
   if (type == 1 && tile_rows == MOE_TM_WIDE) {
     return moe_experts<__nv_bfloat16, MOE_TM_WIDE>(hidden, ld_hidden, w_in, w_out, sorted,
                                                    tile_expert, max_tiles, top, width, ff, limit,
-                                                   alpha, shift, y, ld_y, pair_out, ld_out, s);
+                                                   alpha, shift, single, y, ld_y, pair_out, ld_out, s);
   }
   if (type == 1) {
     return moe_experts<__nv_bfloat16, MOE_TM>(hidden, ld_hidden, w_in, w_out, sorted,
                                               tile_expert, max_tiles, top, width, ff, limit,
-                                              alpha, shift, y, ld_y, pair_out, ld_out, s);
+                                              alpha, shift, single, y, ld_y, pair_out, ld_out, s);
   }
   return AYK_BAD_ARGUMENT;
 }

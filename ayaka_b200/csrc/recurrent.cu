@@ -504,6 +504,120 @@ gla_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int v
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Generalised delta rule with a decay and a removal rate per key channel: per head, with the
+// raw decay z, the raw removal rate y (plus its bias) and the unit key u = k / sqrt(k . k + 1e-6),
+//   w = exp(-decay_rate * sigmoid(z)),   a = sigmoid(y + y_bias),
+//   S <- diag(w) S - (a * u) (u^T S) + k v^T   (both terms read the old S),
+//   out = S^T r,                                S: [N x P].
+// A column of S never meets another: u^T S is one number per column, formed from the old
+// column before it is overwritten (one exchange among the column's lanes), and the answer is a
+// second one. proj rows hold r at 0, k at k_offset, y at a_offset (heads x N each) and v at
+// v_offset (heads x P); z rows hold heads x N raw decays. State of a slot: S as [heads][P][N].
+// The decays, the rates times the key and the key's inverse length are formed in shared
+// memory once per chunk, in fp32.
+template <int RN, int LANES>
+__global__ void __launch_bounds__(SCAN_COLS * LANES)
+delta_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int v_offset,
+                  int a_offset, const float* __restrict__ a_bias, const float* __restrict__ z,
+                  int ld_z, float decay_rate, float* __restrict__ state, long long state_stride,
+                  const int* __restrict__ row_start, const int* __restrict__ state_slot,
+                  float* __restrict__ out, int ld_out, int heads, int N, int P, int chunk,
+                  int vec) {
+  extern __shared__ __align__(16) float scan_smem[];
+  const int stage_floats = chunk * (4 * N + SCAN_COLS + 4);
+  pdl_launch_dependents();
+  const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * SCAN_COLS;
+  const int col = threadIdx.x / LANES, part = threadIdx.x % LANES;
+  const int p = p0 + col;
+  const int r0 = row_start[b], rows = row_start[b + 1] - r0;
+  if (state_slot[b] < 0) return;  // a row of padding (a graph's bucket): no request, no state
+  float* mine = state + (size_t)state_slot[b] * state_stride + (size_t)h * N * P;
+  pdl_wait_for(proj, z, mine);
+  float s[RN];
+#pragma unroll
+  for (int k = 0; k < RN; ++k) {
+    const int n = part + LANES * k;
+    s[k] = (p < P && n < N) ? mine[(size_t)p * N + n] : 0.f;
+  }
+  const int chunks = (rows + chunk - 1) / chunk;
+  auto stage = [&](int c) {
+    float* at = scan_smem + (size_t)(c % SCAN_STAGES) * stage_floats;
+    const int t0 = c * chunk, count = min(chunk, rows - t0);
+    const float* first = proj + (size_t)(r0 + t0) * ld_proj;
+    stage_tile(at, first + h * N, ld_proj, count, N, vec);                                  // r
+    stage_tile(at + (size_t)chunk * N, first + k_offset + h * N, ld_proj, count, N, vec);   // k
+    stage_tile(at + (size_t)2 * chunk * N, z + (size_t)(r0 + t0) * ld_z + h * N, ld_z, count, N,
+               vec);                                                                        // z
+    stage_tile(at + (size_t)3 * chunk * N, first + a_offset + h * N, ld_proj, count, N, vec);  // y
+    stage_columns(at + (size_t)4 * chunk * N, first + v_offset + h * P, ld_proj, count, p0, P,
+                  vec);                                                                     // v
+    copy_commit();
+  };
+  for (int c = 0; c < SCAN_STAGES - 1; ++c) {
+    if (c < chunks) stage(c); else copy_commit();
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (int c = 0; c < chunks; ++c) {
+    if (c + SCAN_STAGES - 1 < chunks) stage(c + SCAN_STAGES - 1); else copy_commit();
+    copy_wait<SCAN_STAGES - 1>();
+    __syncthreads();
+    float* r_s = scan_smem + (size_t)(c % SCAN_STAGES) * stage_floats;
+    float* k_s = r_s + (size_t)chunk * N;
+    float* w_s = k_s + (size_t)chunk * N;   // raw decays, then the factors
+    float* au_s = w_s + (size_t)chunk * N;  // raw rates, then rate * unit key
+    float* v_s = au_s + (size_t)chunk * N;
+    float* inv_s = v_s + (size_t)chunk * SCAN_COLS;  // 1 / length of each row's key
+    const int t0 = c * chunk, count = min(chunk, rows - t0);
+    for (int i = warp; i < count; i += warps) {  // a warp per row: the key's length
+      float ss = 0.f;
+      for (int n = lane; n < N; n += 32) ss = fmaf(k_s[i * N + n], k_s[i * N + n], ss);
+      ss = group_sum<32>(ss);
+      if (lane == 0) inv_s[i] = 1.f / sqrtf(ss + 1e-6f);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < count * N; i += blockDim.x) {
+      const int n = i % N;
+      w_s[i] = expf(-decay_rate / (1.f + expf(-w_s[i])));
+      const float rate = 1.f / (1.f + expf(-(au_s[i] + a_bias[h * N + n])));
+      au_s[i] = rate * k_s[i] * inv_s[i / N];
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int i = 0; i < count; ++i) {
+      const float vv = v_s[i * SCAN_COLS + col];
+      const float* ri = r_s + (size_t)i * N;
+      const float* ki = k_s + (size_t)i * N;
+      const float* wi = w_s + (size_t)i * N;
+      const float* ai = au_s + (size_t)i * N;
+      float seen = 0.f;  // k . (old column); times the inverse length: u . (old column)
+#pragma unroll
+      for (int k = 0; k < RN; ++k) {
+        const int n = part + LANES * k;
+        if (n < N) seen = fmaf(ki[n], s[k], seen);
+      }
+      seen = group_sum<LANES>(seen) * inv_s[i];
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < RN; ++k) {
+        const int n = part + LANES * k;
+        if (n < N) {
+          s[k] = fmaf(wi[n], s[k], fmaf(ki[n], vv, -ai[n] * seen));
+          acc = fmaf(s[k], ri[n], acc);
+        }
+      }
+      const float sum = group_sum<LANES>(acc);
+      if (part == 0 && p < P) out[(size_t)(r0 + t0 + i) * ld_out + h * P + p] = sum;
+    }
+    __syncthreads();  // the buffer is staged again at the next turn
+  }
+#pragma unroll
+  for (int k = 0; k < RN; ++k) {
+    const int n = part + LANES * k;
+    if (p < P && n < N) mine[(size_t)p * N + n] = s[k];
+  }
+}
+
 // rows of a chunk (at most 32: a warp scans a chunk's gates), and the ring's bytes: up to
 // 68 KB, which a kernel has to be allowed once (allow_smem)
 inline int scan_chunk(int n) { return n <= 64 ? 32 : (n <= 128 ? 16 : (n <= 256 ? 8 : 4)); }
@@ -676,4 +790,52 @@ AYK_API int ayk_gla_scan(const float* proj, int ld_proj, int k_offset, int v_off
   if (N <= 256) AYK_GLA(8, 32);
   AYK_GLA(16, 32);
 #undef AYK_GLA
+}
+
+// rows of a chunk of the delta-rule scan (four staged tiles of N entries a row)
+static inline int delta_chunk(int n) { return n <= 32 ? 32 : (n <= 64 ? 16 : (n <= 128 ? 8 : 4)); }
+
+// See delta_scan_kernel. `a_bias`: heads x N floats. decay_rate: the factor on sigmoid(z) in
+// the decay's exponent.
+AYK_API int ayk_delta_scan(const float* proj, int ld_proj, int k_offset, int v_offset,
+                           int a_offset, const float* a_bias, const float* z, int ld_z,
+                           float decay_rate, float* state, long long state_stride,
+                           const int* row_start, const int* state_slot, float* out, int ld_out,
+                           int requests, int heads, int N, int P, void* stream) {
+  using namespace ayk;
+  if (requests == 0) return AYK_OK;
+  const int tiles = (P + SCAN_COLS - 1) / SCAN_COLS;
+  if (requests < 0 || heads < 1 || N < 1 || P < 1 || proj == nullptr || z == nullptr ||
+      a_bias == nullptr || state == nullptr || row_start == nullptr || state_slot == nullptr ||
+      out == nullptr || !(decay_rate >= 0.f) || ld_out < heads * P || ld_z < heads * N ||
+      requests > 65535 || k_offset < 0 || v_offset < 0 || a_offset < 0 ||
+      ld_proj < max(max(k_offset, a_offset) + heads * N, v_offset + heads * P) ||
+      state_stride < (long long)heads * N * P) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (N > SCAN_MAX_N || tiles > 65535) return AYK_TOO_LARGE;
+  const int chunk = delta_chunk(N);
+  const size_t smem = (size_t)SCAN_STAGES * chunk * (4 * N + SCAN_COLS + 4) * sizeof(float);
+  int vec = scan_vec(proj, ld_proj, N, P, {k_offset, v_offset, a_offset});
+  if (((uintptr_t)z % 16) != 0 || ld_z % 4 != 0) vec = 1;
+  const dim3 grid(heads, requests, tiles);
+#define AYK_DELTA(RN, LANES)                                                                   \
+  {                                                                                            \
+    static const bool allowed =                                                                \
+        (cudaFuncSetAttribute(delta_scan_kernel<RN, LANES>,                                    \
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, 144 * 1024), true); \
+    (void)allowed;                                                                             \
+    return launch_kernel(delta_scan_kernel<RN, LANES>, grid, dim3(SCAN_COLS * LANES), smem,    \
+                         (cudaStream_t)stream, 1, proj, ld_proj, k_offset, v_offset, a_offset, \
+                         a_bias, z, ld_z, decay_rate, state, state_stride, row_start,          \
+                         state_slot, out, ld_out, heads, N, P, chunk, vec);                    \
+  }
+  if (N <= 8) AYK_DELTA(1, 8);
+  if (N <= 16) AYK_DELTA(2, 8);
+  if (N <= 32) AYK_DELTA(4, 8);
+  if (N <= 64) AYK_DELTA(4, 16);
+  if (N <= 128) AYK_DELTA(4, 32);
+  if (N <= 256) AYK_DELTA(8, 32);
+  AYK_DELTA(16, 32);
+#undef AYK_DELTA
 }

@@ -27,6 +27,7 @@ __all__ = [
     "cast_rows",
     "causal_conv_silu",
     "decode_splits",
+    "delta_scan",
     "embed_rows",
     "gated_attention",
     "gated_attention_prepare",
@@ -57,6 +58,10 @@ __all__ = [
     "moe_tile_rows",
     "norm_add",
     "norm_sum",
+    "pool_slots",
+    "pooled_attention",
+    "pooled_blocks",
+    "pooled_prepare",
     "rms_norm",
     "rope",
     "rope_frequencies",
@@ -69,6 +74,7 @@ __all__ = [
     "talking_attention",
     "talking_prepare",
     "timed",
+    "unary_rows",
 ]
 
 ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2}
@@ -82,6 +88,11 @@ BF16_GEMM = "tcgen05"
 #: Whether parts that can hand a layer half (or a run of layers) to the C++ host code
 #: (``csrc/step_host.cu``) do so; tests switch it off to compare the two paths bit by bit.
 NATIVE_STEP = True
+
+#: How :class:`~ayaka_b200.parts.pooled_attention.PooledWindowAttention` runs bfloat16 prompt
+#: portions: ``"mma"`` (the flash kernel on the tensor cores) or ``"generic"`` (one CTA per
+#: row and head on the CUDA cores); tests switch it to compare the two.
+POOLED_PREFILL = "generic"
 
 _launches = 0
 
@@ -111,7 +122,8 @@ _TIMED = ("embed_rows", "layer_norm", "linear", "linear_kv", "kv_store", "attent
           "causal_conv_silu", "mamba2_scan",
           "mlstm_scan", "gla_scan", "talking_prepare", "talking_attention", "norm_sum",
           "moe_route", "moe_experts", "moe_join", "moe_route_scored", "cast_rows", "gated_unit",
-          "norm_add", "gated_attention_prepare", "gated_attention", "gated_decode")
+          "norm_add", "gated_attention_prepare", "gated_attention", "gated_decode",
+          "unary_rows", "delta_scan", "pooled_prepare", "pooled_blocks", "pooled_attention")
 
 
 @contextlib.contextmanager
@@ -1377,10 +1389,11 @@ def moe_scratch(rows: int, experts: int, top: int) -> tuple[int, int]:
 
 
 def moe_route(logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, *, top: int,
-              rows: int) -> None:
+              rows: int, over_all: bool = False) -> None:
     """Per row of float32 ``logits`` ``[N, experts]``: the ``top`` largest (ties to the smaller
     index), in descending order, into ``chosen`` (int32 ``[N * top]``), and the softmax over
-    just those into ``share`` (float32 ``[N * top]``)."""
+    just those into ``share`` (float32 ``[N * top]``); with ``over_all`` the chosen ones' part
+    of the softmax over every expert instead (shares that do not add up to one)."""
     op = "moe_route"
     if _left_out and op in _left_out:
         return
@@ -1391,7 +1404,7 @@ def moe_route(logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, *
         raise BackendError(f"{op}: shapes do not fit")
     status = library("moe").ayk_moe_route(
         _ptr(logits), c_int(logits.stride(0)), c_int(rows), c_int(logits.shape[1]), c_int(top),
-        _ptr(chosen), _ptr(share), _stream())
+        c_int(1 if over_all else 0), _ptr(chosen), _ptr(share), _stream())
     check(status, op)
 
 
@@ -1399,7 +1412,7 @@ def moe_experts(hidden: torch.Tensor, w_in: torch.Tensor, w_out: torch.Tensor,
                 chosen: torch.Tensor, pair_out: torch.Tensor, *, experts: int, top: int,
                 limit: float, alpha: float, sorted_pairs: torch.Tensor,
                 tile_expert: torch.Tensor, inner: torch.Tensor, rows: int,
-                shift: float = 1.0) -> None:
+                shift: float = 1.0, single: bool = False) -> None:
     """The chosen experts of every row, as two products grouped by expert. ``w_in``
     ``[experts * 2 * ff, width]`` holds each expert's gate rows, then its up rows; ``w_out``
     ``[experts * width, ff]`` its down matrix. Pair ``p = row * top + choice`` computes
@@ -1407,7 +1420,8 @@ def moe_experts(hidden: torch.Tensor, w_in: torch.Tensor, w_out: torch.Tensor,
     ``y = g * sigmoid(alpha * g) * (u + shift)`` and ``pair_out[p] = W_down y`` (float32
     ``[N * top, width]``, unweighted); ``limit=inf, alpha=1, shift=0`` is ``silu(g) * u``. Scratch: ``sorted_pairs`` (int32, ``tiles * tile
     rows``), ``tile_expert`` (int32, ``tiles``) and ``inner`` (``[tiles * tile rows, ff]``,
-    compute dtype) sized by :func:`moe_scratch`."""
+    compute dtype) sized by :func:`moe_scratch`. With ``single`` an expert has no gate:
+    ``w_in`` is ``[experts * ff, width]`` and ``y = relu(W_up h)^2``."""
     op = "moe_experts"
     if _left_out and op in _left_out:
         return
@@ -1423,7 +1437,7 @@ def moe_experts(hidden: torch.Tensor, w_in: torch.Tensor, w_out: torch.Tensor,
     tile_rows = moe_tile_rows(rows, experts, top, hidden.dtype)
     tiles = moe_max_tiles(rows, experts, top, tile_rows)
     if hidden.dtype not in _TYPE or not w_in.is_contiguous() or not w_out.is_contiguous() or \
-            tuple(w_in.shape) != (experts * 2 * ff, width) or \
+            tuple(w_in.shape) != (experts * (1 if single else 2) * ff, width) or \
             tuple(w_out.shape) != (experts * width, ff) or inner.shape[1] != ff or \
             pair_out.shape[1] != width or rows > hidden.shape[0] or \
             chosen.shape[0] < rows * top or pair_out.shape[0] < rows * top or \
@@ -1435,7 +1449,8 @@ def moe_experts(hidden: torch.Tensor, w_in: torch.Tensor, w_out: torch.Tensor,
     status = library("moe").ayk_moe_experts(
         _ptr(hidden), c_int(hidden.stride(0)), _ptr(w_in), _ptr(w_out), _ptr(chosen),
         c_int(rows), c_int(experts), c_int(top), c_int(width), c_int(ff), c_float(limit),
-        c_float(alpha), c_float(shift), _ptr(sorted_pairs), _ptr(tile_expert), c_int(tiles),
+        c_float(alpha), c_float(shift), c_int(1 if single else 0), _ptr(sorted_pairs),
+        _ptr(tile_expert), c_int(tiles),
         c_int(tile_rows),
         _ptr(inner),
         c_int(inner.stride(0)), _ptr(pair_out), c_int(pair_out.stride(0)),
@@ -1546,6 +1561,236 @@ def gated_unit(gate: torch.Tensor, out: torch.Tensor, *, activation: str, rows: 
         c_int(GATE_ACTIVATIONS[activation]), _ptr(out), c_int(out.stride(0)), c_int(rows),
         c_int(width), c_int(_TYPE[out.dtype]), _stream())
     check(status, op)
+
+
+UNARY_ACTIVATIONS = {"tanh": 0, "xielu": 1}
+
+
+def unary_rows(x: torch.Tensor, out: torch.Tensor, *, activation: str, rows: int,
+               bias: torch.Tensor | None = None, numbers: torch.Tensor | None = None) -> None:
+    """``out = act(x + bias)`` entry by entry in fp32 (``x`` float32 ``[N, width]``, ``out``
+    float32 or bfloat16). ``act``: ``tanh``, or ``xielu`` with ``numbers`` = float32 ``(p, q)``:
+    ``softplus(p) z^2 + z / 2`` for ``z > 0``, ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2``
+    otherwise."""
+    op = "unary_rows"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "x", x, torch.float32, 2)
+    _need(op, "out", out, ndim=2)
+    width = out.shape[1]
+    if out.dtype not in _TYPE or activation not in UNARY_ACTIVATIONS or x.shape[1] != width \
+            or rows > x.shape[0] or rows > out.shape[0]:
+        raise BackendError(f"{op}: shapes, types or arguments do not fit")
+    if bias is not None:
+        _need(op, "bias", bias, torch.float32, 1)
+        if bias.shape[0] != width:
+            raise BackendError(f"{op}: the bias does not match the width")
+    if activation == "xielu":
+        _need(op, "numbers", numbers, torch.float32, 1)
+        if numbers.shape[0] != 2:
+            raise BackendError(f"{op}: xielu takes two numbers")
+    status = library("gated").ayk_unary_rows(
+        _ptr(x), c_int(x.stride(0)), _ptr(bias), c_int(UNARY_ACTIVATIONS[activation]),
+        _ptr(numbers), _ptr(out), c_int(out.stride(0)), c_int(rows), c_int(width),
+        c_int(_TYPE[out.dtype]), _stream())
+    check(status, op)
+
+
+def delta_scan(proj: torch.Tensor, decay: torch.Tensor, rate_bias: torch.Tensor,
+               state: torch.Tensor, out: torch.Tensor, *, row_start: torch.Tensor,
+               state_slot: torch.Tensor, requests: int, heads: int, dim: int, columns: int,
+               k_offset: int, v_offset: int, a_offset: int, decay_rate: float) -> None:
+    """The generalised delta rule over the step's rows, request by request, from and into each
+    request's slot of ``state`` (float32 ``[slots, heads * columns * dim]``, ``S`` kept as
+    ``[head][column][key channel]``). ``proj`` (float32) holds per row the receptance at column
+    0, the key at ``k_offset``, the raw removal rate at ``a_offset`` (``heads x dim`` each) and
+    the value at ``v_offset`` (``heads x columns``); ``decay`` (float32 ``[N, heads * dim]``)
+    the raw decays. Per head, with ``u = k / sqrt(k . k + 1e-6)``,
+    ``w = exp(-decay_rate * sigmoid(decay))`` and ``a = sigmoid(rate + rate_bias)``:
+    ``S <- diag(w) S - (a * u)(u^T S) + k v^T`` (both terms from the old ``S``) and
+    ``out = S^T r`` (float32 ``[N, heads * columns]``)."""
+    op = "delta_scan"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "proj", proj, torch.float32, 2)
+    _need(op, "decay", decay, torch.float32, 2)
+    _need(op, "rate_bias", rate_bias, torch.float32, 1)
+    _need(op, "state", state, torch.float32, 2)
+    _need(op, "out", out, torch.float32, 2)
+    _need(op, "row_start", row_start, torch.int32, 1)
+    _need(op, "state_slot", state_slot, torch.int32, 1)
+    if rate_bias.shape[0] != heads * dim or decay.shape[1] < heads * dim or \
+            out.shape[1] < heads * columns or state.shape[1] < heads * dim * columns or \
+            row_start.shape[0] < requests + 1 or state_slot.shape[0] < requests:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("recurrent").ayk_delta_scan(
+        _ptr(proj), c_int(proj.stride(0)), c_int(k_offset), c_int(v_offset), c_int(a_offset),
+        _ptr(rate_bias), _ptr(decay), c_int(decay.stride(0)), c_float(decay_rate), _ptr(state),
+        c_longlong(state.stride(0)), _ptr(row_start), _ptr(state_slot), _ptr(out),
+        c_int(out.stride(0)), c_int(requests), c_int(heads), c_int(dim), c_int(columns),
+        _stream())
+    check(status, op)
+
+
+def pooled_prepare(proj: torch.Tensor, *, k_offset: int, q_weight: torch.Tensor | None,
+                   k_weight: torch.Tensor | None, eps: float, positions: torch.Tensor,
+                   freq: torch.Tensor | None, rot_dims: int, rot_gain: float,
+                   slot_mapping: torch.Tensor | None, k_pages: torch.Tensor | None,
+                   v_pages: torch.Tensor | None, q: torch.Tensor, heads: int, kv_heads: int,
+                   dim: int, rows: int) -> None:
+    """From a row of the fused projection (float32: queries at column 0, keys at
+    ``k_offset``): every head divided by its own root mean square and multiplied by one weight
+    of ``dim`` entries shared by the heads (``q_weight`` / ``k_weight``; ``None``: no norm),
+    the first ``rot_dims`` entries of each head rotated by the row's position (entry ``i`` with
+    ``i + rot_dims / 2``, cosine and sine times ``rot_gain``); queries into ``q``, keys into the
+    row's slot of ``k_pages`` and the *raw* key rows (before norm and rotation) into
+    ``v_pages`` as the token's value."""
+    op = "pooled_prepare"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "proj", proj, torch.float32, 2)
+    _need(op, "q", q, ndim=2)
+    _need(op, "positions", positions, torch.int32, 1)
+    if q.dtype not in _TYPE or rows > proj.shape[0] or rows > q.shape[0] or \
+            rows > positions.shape[0] or q.shape[1] != heads * dim or \
+            proj.shape[1] < k_offset + kv_heads * dim:
+        raise BackendError(f"{op}: shapes do not fit")
+    page_size = 0
+    if k_pages is not None:
+        _need(op, "k_pages", k_pages, q.dtype, 4)
+        _need(op, "slot_mapping", slot_mapping, torch.int32, 1)
+        if not k_pages.is_contiguous() or tuple(k_pages.shape[1:]) != \
+                (kv_heads, k_pages.shape[2], dim) or rows > slot_mapping.shape[0]:
+            raise BackendError(f"{op}: the key pages do not fit")
+        page_size = k_pages.shape[2]
+        if v_pages is not None:
+            _need(op, "v_pages", v_pages, q.dtype, 4)
+            if not v_pages.is_contiguous() or tuple(v_pages.shape) != tuple(k_pages.shape):
+                raise BackendError(f"{op}: raw keys as values need value pages like the key "
+                                   "pages")
+    if rot_dims:
+        _need(op, "freq", freq, torch.float64, 1)
+        if freq.shape[0] != rot_dims // 2:
+            raise BackendError(f"{op}: one frequency per rotated pair")
+    for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if weight is not None:
+            _need(op, name, weight, torch.float32, 1)
+            if weight.shape[0] != dim:
+                raise BackendError(f"{op}: the norm weights have one entry per head entry")
+    status = library("pooled_attention").ayk_pooled_prepare(
+        _ptr(proj), c_int(proj.stride(0)), c_int(k_offset), _ptr(q_weight), _ptr(k_weight),
+        c_float(eps), _ptr(positions), _ptr(freq), c_int(rot_dims), c_float(rot_gain),
+        _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages), c_int(page_size), _ptr(q),
+        c_int(q.stride(0)), c_int(rows), c_int(heads), c_int(kv_heads), c_int(dim),
+        c_int(_TYPE[q.dtype]), _stream())
+    check(status, op)
+
+
+def pool_slots(page_size: int, pool: int) -> int:
+    """Pooled rows a page of ``page_size`` tokens holds for blocks of ``pool`` tokens."""
+    return -(-page_size // pool)
+
+
+def pooled_blocks(k_pages: torch.Tensor, v_pages: torch.Tensor, k_pool: torch.Tensor,
+                  v_pool: torch.Tensor, block_table: torch.Tensor, request_of_row: torch.Tensor,
+                  positions: torch.Tensor, *, pool: int, rows: int) -> None:
+    """For every row of the step whose position is the last of a block of ``pool`` positions:
+    the mean of the block's cached keys into ``k_pool`` and of its cached values into
+    ``v_pool`` (``[pages, kv_heads, pool_slots, dim]``), in the page of the block's first
+    position, at slot ``(first % page_size) // pool``."""
+    op = "pooled_blocks"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "k_pages", k_pages, ndim=4)
+    _need(op, "v_pages", v_pages, k_pages.dtype, 4)
+    _need(op, "k_pool", k_pool, k_pages.dtype, 4)
+    _need(op, "v_pool", v_pool, k_pages.dtype, 4)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "request_of_row", request_of_row, torch.int32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    pages, kv_heads, page_size, dim = k_pages.shape
+    vdim = v_pages.shape[3]
+    slots = pool_slots(page_size, pool) if pool > 0 else 0
+    if k_pages.dtype not in _TYPE or pool < 1 or \
+            tuple(k_pool.shape) != (pages, kv_heads, slots, dim) or \
+            tuple(v_pool.shape) != (pages, kv_heads, slots, vdim) or \
+            not all(t.is_contiguous() for t in (k_pages, v_pages, k_pool, v_pool)) or \
+            rows > positions.shape[0] or rows > request_of_row.shape[0]:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("pooled_attention").ayk_pooled_blocks(
+        _ptr(positions), _ptr(request_of_row), _ptr(block_table), c_int(block_table.stride(0)),
+        _ptr(k_pages), _ptr(v_pages), _ptr(k_pool), _ptr(v_pool), c_int(page_size), c_int(pool),
+        c_int(slots), c_int(rows), c_int(kv_heads), c_int(dim), c_int(vdim),
+        c_int(_TYPE[k_pages.dtype]), _stream())
+    check(status, op)
+
+
+def pooled_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     k_pool: torch.Tensor | None, v_pool: torch.Tensor | None,
+                     block_table: torch.Tensor, request_of_row: torch.Tensor,
+                     positions: torch.Tensor, out: torch.Tensor, *, heads: int, scale: float,
+                     window: int, pool: int, sink: torch.Tensor | None, rows: int,
+                     shares: int = 0, partial: torch.Tensor | None = None) -> bool:
+    """Softmax attention of ``rows`` rows over the paged cache: the row at position ``p`` sees
+    the keys ``j`` with ``0 <= p - j < window`` (``window`` 0: all earlier keys) and, with
+    ``pool`` > 0, the pooled rows of the blocks ``e < (p - window + 1) // pool``; the
+    denominator also holds ``exp(sink[head])`` when ``sink`` (float32 ``[heads]``) is given.
+    ``shares`` 0: one CTA per (row, head), any sizes; ``shares`` >= 1: a row's entries cut into
+    that many shares (``partial``: float32 scratch of ``rows * heads * shares * (vdim + 2)``
+    elements when more than one). Returns False, having run nothing, when the kernel of
+    shares does not take the sizes."""
+    global _launches
+    op = "pooled_attention"
+    if _left_out and op in _left_out:
+        return True
+    _need(op, "q", q, ndim=2)
+    _need(op, "out", out, q.dtype, 2)
+    _need(op, "k_pages", k_pages, q.dtype, 4)
+    _need(op, "v_pages", v_pages, q.dtype, 4)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "request_of_row", request_of_row, torch.int32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    if q.dtype not in _TYPE or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise BackendError(f"{op}: contiguous float32 or bfloat16 pages only")
+    pages, kv_heads, page_size, dim = k_pages.shape
+    vdim = v_pages.shape[3]
+    if q.shape[1] != heads * dim or out.shape[1] != heads * vdim or \
+            tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3]) or rows > out.shape[0] or \
+            rows > q.shape[0] or rows > request_of_row.shape[0] or \
+            rows > positions.shape[0] or heads % kv_heads or shares < 0:
+        raise BackendError(f"{op}: shapes do not fit")
+    slots = 0
+    if pool > 0 and window > 0:
+        slots = pool_slots(page_size, pool)
+        _need(op, "k_pool", k_pool, q.dtype, 4)
+        _need(op, "v_pool", v_pool, q.dtype, 4)
+        if tuple(k_pool.shape) != (pages, kv_heads, slots, dim) or \
+                tuple(v_pool.shape) != (pages, kv_heads, slots, vdim) or \
+                not k_pool.is_contiguous() or not v_pool.is_contiguous():
+            raise BackendError(f"{op}: the pooled rows do not match the pages")
+    if sink is not None:
+        _need(op, "sink", sink, torch.float32, 1)
+        if sink.shape[0] != heads:
+            raise BackendError(f"{op}: one sink per head")
+    if shares > 1:
+        if partial is None:
+            raise BackendError(f"{op}: more than one share needs scratch")
+        _need(op, "partial", partial, torch.float32)
+        if partial.numel() < rows * heads * shares * (vdim + 2):
+            raise BackendError(f"{op}: the scratch is too small")
+    status = library("pooled_attention").ayk_pooled_attention(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(k_pool), _ptr(v_pool),
+        _ptr(block_table), c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions),
+        _ptr(sink), _ptr(partial if shares > 1 else None), _ptr(out), c_int(out.stride(0)),
+        c_int(rows), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(page_size),
+        c_float(scale), c_int(window), c_int(pool), c_int(slots), c_int(shares),
+        c_int(_TYPE[q.dtype]), _stream())
+    if status == -6:  # the kernel of shares does not take these sizes
+        return False
+    check(status, op)
+    if shares > 1:
+        _launches += 1  # the merge
+    return True
 
 
 def norm_add(x: torch.Tensor, weight: torch.Tensor, eps: float, dst: torch.Tensor, *,

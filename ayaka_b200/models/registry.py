@@ -81,4 +81,5 @@ def _builtin() -> None:
     import ayaka_b200.models.gpt2  # noqa: F401  (registers itself)
     import ayaka_b200.models.gagotar  # noqa: F401
     import ayaka_b200.models.mapuvik  # noqa: F401
+    import ayaka_b200.models.rizitar  # noqa: F401
     import ayaka_b200.models.semadra  # noqa: F401

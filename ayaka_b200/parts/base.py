@@ -46,6 +46,9 @@ class CacheNeed:
     chunk: int = 0  # n > 0: only keys of the query's own block of n positions (from 0)
     value_dim: int = 0  # entries of a value row when they differ from a key's (0: head_dim)
     keep_first: int = 0  # with a window: the first n keys of the sequence stay in sight
+    #: n > 0: beside every page, rows for the means of blocks of n tokens (one key and one
+    #: value row per block, in the page of the block's first token)
+    pool: int = 0
 
     @property
     def value_head_dim(self) -> int:

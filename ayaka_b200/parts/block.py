@@ -9,7 +9,7 @@ from ayaka_b200.parts.base import BuildContext, Part, build_part, register_part
 from ayaka_b200.parts.context import LayerCache, StepContext, Workspace
 from ayaka_b200.parts.spec import LayerSpec
 
-__all__ = ["Block", "OutputNormBlock", "ParallelBlock", "PreNormBlock"]
+__all__ = ["Block", "OutputNormBlock", "ParallelBlock", "PreNormBlock", "SandwichNormBlock"]
 
 
 class Block(Part):
@@ -215,3 +215,76 @@ class OutputNormBlock(Block):
         if self.side is not None:
             self.side.forward(stream, residual, step, factor=self.factor,  # type: ignore
                               copy=copy)
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Block):
+    """``x += post1(mixer(pre1(x))); x += post2(feed_forward(pre2(x)))`` and, with a ``side``
+    part, ``x += f * side(x)``: a norm in front of every sublayer and another on its output.
+    The norms in front are ``spec.mixer_norm`` / ``spec.feed_forward_norm`` (children
+    ``mixer_norm``, ``feed_forward_norm``); the ones behind have the same kind and sizes and
+    weights of their own (children ``mixer_post_norm``, ``feed_forward_post_norm``). ``f`` is
+    ``spec.residual_factor`` and stands on everything that joins the stream.
+
+    The stream is fp32. A sublayer reads its norm's output in the compute type and writes a
+    fp32 branch (``forward_into`` where the part has it, else a zeroed branch it adds into);
+    the norm behind it adds ``f * norm(branch)`` to the stream in one launch, and for a side
+    part that launch also leaves the new stream rounded once to the compute type."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext, position: Part | None) -> None:
+        super().__init__(ctx)
+        has_ff = spec.feed_forward.kind != "none"
+
+        def norm(name: str, part: object) -> Part:
+            return self.add_child(name, build_part("norm", part.kind, part, ctx))  # type: ignore
+
+        self.mixer_norm = norm("mixer_norm", spec.mixer_norm)
+        self.mixer = self.add_child(
+            "mixer", build_part("mixer", spec.mixer.kind, spec.mixer, ctx, position))
+        self.mixer_post_norm = norm("mixer_post_norm", spec.mixer_norm)
+        self.feed_forward_norm = norm("feed_forward_norm", spec.feed_forward_norm) \
+            if has_ff else None
+        self.feed_forward = self.add_child(
+            "feed_forward",
+            build_part("feed_forward", spec.feed_forward.kind, spec.feed_forward, ctx))
+        self.feed_forward_post_norm = norm("feed_forward_post_norm", spec.feed_forward_norm) \
+            if has_ff else None
+        self.side = None if spec.side is None else self.add_child(
+            "side", build_part("side", spec.side.kind, spec.side, ctx))
+        self.width = int(spec.mixer_norm.width)  # type: ignore[arg-type]
+        self.factor = float(spec.residual_factor)
+        for post in (self.mixer_post_norm, self.feed_forward_post_norm):
+            if post is not None and not hasattr(post, "add_normed"):
+                raise ValueError("a sandwich_norm block needs norms that can add their result "
+                                 "to the stream (add_normed)")
+
+    def forward(self, residual: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
+        n, work = step.num_rows, step.workspace
+        rounded = self.ctx.dtype != torch.float32
+        hidden = work.buffer("block.normed", self.width, self.ctx.dtype)
+        branch = work.buffer("block.branch", self.width, torch.float32)
+        # the side part reads the stream itself: the last norm behind a sublayer leaves it a
+        # copy in the compute type (in float32 it reads the stream)
+        copy = work.buffer("block.stream", self.width, self.ctx.dtype) \
+            if rounded and self.side is not None else None
+        last_is_mixer = self.feed_forward_norm is None
+        self.mixer_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
+        if hasattr(self.mixer, "forward_into"):
+            self.mixer.forward_into(hidden, branch, step, cache)  # type: ignore[attr-defined]
+        else:
+            branch[:n].zero_()
+            self.mixer.forward(hidden, branch, step, cache)  # type: ignore[attr-defined]
+        self.mixer_post_norm.add_normed(branch, residual, factor=self.factor,  # type: ignore
+                                        count=n, copy=copy if last_is_mixer else None)
+        if self.feed_forward_norm is not None:
+            self.feed_forward_norm.forward(residual, hidden, count=n)  # type: ignore
+            if hasattr(self.feed_forward, "forward_into"):
+                self.feed_forward.forward_into(hidden, branch, step)  # type: ignore
+            else:
+                branch[:n].zero_()
+                self.feed_forward.forward(hidden, branch, step)  # type: ignore[attr-defined]
+            self.feed_forward_post_norm.add_normed(  # type: ignore[union-attr]
+                branch, residual, factor=self.factor, count=n, copy=copy)
+        if self.side is not None:
+            self.side.forward(copy if rounded else residual, residual, step,  # type: ignore
+                              factor=self.factor)

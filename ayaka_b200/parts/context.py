@@ -62,6 +62,8 @@ class LayerCache:
     v_pages: torch.Tensor | None
     writes: bool  # False when this run reads the cache another run wrote
     state: torch.Tensor | None = None  # [max_requests, *StateNeed.shape]
+    k_pool: torch.Tensor | None = None  # [pages, kv_heads, pooled slots, head_dim]
+    v_pool: torch.Tensor | None = None
 
 
 @dataclass(slots=True)

@@ -36,10 +36,15 @@ class MixtureOfExperts(FeedForward):
     With ``shared_inner`` a gated feed-forward of that inner width (child ``shared``, the same
     unit) runs for every row and is added.
 
+    With ``scoring="softmax_all"`` the scores are the softmax over *all* experts, the ``top``
+    largest are chosen and weighted by their scores as they are (no renormalising). With
+    ``unit="relu_squared"`` an expert has no gate: ``W_down relu(W_up h)^2``, and ``in.weight``
+    is ``[experts * inner, width]``.
+
     Spec parameters: ``width``, ``experts``, ``top``, ``inner``; ``unit`` (``clamped`` when
-    absent, with ``limit`` and ``alpha``; or ``silu``); ``scoring`` (``softmax`` when absent;
-    or ``sigmoid`` with ``groups``, ``keep_groups``, ``route_scale``, ``renormalise``);
-    ``shared_inner`` (0 when absent).
+    absent, with ``limit`` and ``alpha``; or ``silu``; or ``relu_squared``); ``scoring``
+    (``softmax`` when absent; ``softmax_all``; or ``sigmoid`` with ``groups``, ``keep_groups``,
+    ``route_scale``, ``renormalise``); ``shared_inner`` (0 when absent).
     """
 
     def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
@@ -49,7 +54,8 @@ class MixtureOfExperts(FeedForward):
         self.top = int(spec.top)  # type: ignore[arg-type]
         self.inner = int(spec.inner)  # type: ignore[arg-type]
         self.unit = str(spec.get("unit", "clamped"))
-        if self.unit == "silu":
+        self.single = self.unit == "relu_squared"
+        if self.unit in ("silu", "relu_squared"):
             self.limit, self.alpha, self.shift = float("inf"), 1.0, 0.0
         elif self.unit == "clamped":
             self.limit = float(spec.limit)  # type: ignore[arg-type]
@@ -65,7 +71,7 @@ class MixtureOfExperts(FeedForward):
         self.keep_groups = int(spec.get("keep_groups", self.groups))  # type: ignore[arg-type]
         self.route_scale = float(spec.get("route_scale", 1.0))  # type: ignore[arg-type]
         self.renormalise = bool(spec.get("renormalise", False))
-        if self.scoring not in ("softmax", "sigmoid"):
+        if self.scoring not in ("softmax", "softmax_all", "sigmoid"):
             raise ValueError(f"unknown router scoring {self.scoring!r}")
         if self.scoring == "sigmoid" and (
                 self.groups < 1 or self.experts % self.groups
@@ -74,8 +80,9 @@ class MixtureOfExperts(FeedForward):
             raise ValueError("groups must divide experts, 1 <= keep_groups <= groups, and the "
                              "kept groups must hold at least top experts")
         self.router = self.add_param("router.weight", (self.experts, self.width), "matrix")
-        self.in_weight = self.add_param("in.weight", (self.experts * 2 * self.inner, self.width),
-                                        "matrix")
+        self.in_weight = self.add_param(
+            "in.weight", (self.experts * (1 if self.single else 2) * self.inner, self.width),
+            "matrix")
         self.out_weight = self.add_param("out.weight", (self.experts * self.width, self.inner),
                                          "matrix")
         shared_inner = int(spec.get("shared_inner", 0))  # type: ignore[arg-type]
@@ -114,11 +121,12 @@ class MixtureOfExperts(FeedForward):
                                  keep=self.keep_groups, factor=self.route_scale,
                                  renormalise=self.renormalise, rows=n)
         else:
-            ops.moe_route(logits, chosen, share, top=top, rows=n)
+            ops.moe_route(logits, chosen, share, top=top, rows=n,
+                          over_all=self.scoring == "softmax_all")
         ops.moe_experts(hidden, self.in_weight, self.out_weight, chosen, pair_out,
                         experts=self.experts, top=top, limit=self.limit, alpha=self.alpha,
                         shift=self.shift, sorted_pairs=sorted_pairs, tile_expert=tile_expert,
-                        inner=inner, rows=n)
+                        inner=inner, rows=n, single=self.single)
         ops.moe_join(pair_out, share, residual, top=top, scale=scale, accumulate=accumulate,
                      rows=n)
         if self.shared is not None:

@@ -37,8 +37,13 @@ class DenseMLP(FeedForward):
     """``residual += act(h @ Wup.T + b_up) @ Wdown.T + b_down`` with the activation evaluated
     in fp32 inside the first product's epilogue (``python/ayaka/layers/ffn/dense.py:22-57``).
 
-    Spec parameters: ``width``, ``inner``, ``activation`` (``gelu_tanh`` or ``gelu_erf``),
-    ``bias`` (bool).
+    With ``activation="xielu"`` the unit is ``softplus(p) z^2 + z / 2`` for ``z > 0`` and
+    ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2`` otherwise, with two learned numbers
+    (parameter ``act.numbers`` = ``(p, q)``): the first product writes fp32, one element-wise
+    launch adds the bias and applies the unit.
+
+    Spec parameters: ``width``, ``inner``, ``activation`` (``gelu_tanh``, ``gelu_erf`` or
+    ``xielu``), ``bias`` (bool).
     """
 
     def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
@@ -46,25 +51,45 @@ class DenseMLP(FeedForward):
         self.width = int(spec.width)  # type: ignore[arg-type]
         self.inner = int(spec.inner)  # type: ignore[arg-type]
         self.activation = str(spec.activation)
-        if self.activation not in ops.ACTIVATIONS or self.activation == "none":
+        self.learned_unit = self.activation == "xielu"
+        if not self.learned_unit and (self.activation not in ops.ACTIVATIONS
+                                      or self.activation == "none"):
             raise ValueError(f"unknown activation {self.activation!r}")
         bias = bool(spec.get("bias", True))
         self.up_weight = self.add_param("up.weight", (self.inner, self.width), "matrix")
         self.up_bias = self.add_param("up.bias", (self.inner,), "vector") if bias else None
         self.down_weight = self.add_param("down.weight", (self.width, self.inner), "matrix")
         self.down_bias = self.add_param("down.bias", (self.width,), "vector") if bias else None
+        self.numbers = self.add_param("act.numbers", (2,), "vector") if self.learned_unit \
+            else None
         self._native: dict[tuple[int, int], object] = {}
 
     def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext) -> None:
+        self._run(hidden, residual, step, accumulate=True)
+
+    def forward_into(self, hidden: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        """The same, written into ``out`` (fp32 ``[N, width]``) instead of added to it."""
+        self._run(hidden, out, step, accumulate=False)
+
+    def _run(self, hidden: torch.Tensor, out: torch.Tensor, step: StepContext,
+             accumulate: bool) -> None:
         n = step.num_rows
         inner = step.workspace.buffer("feed_forward.inner", self.inner, self.ctx.dtype)
-        ops.linear(hidden, self.up_weight, self.up_bias, inner, activation=self.activation,
-                   rows=n)
-        ops.linear(inner, self.down_weight, self.down_bias, residual, residual=True, rows=n)
+        if self.learned_unit:
+            raw = step.workspace.buffer("feed_forward.raw", self.inner, torch.float32)
+            ops.linear(hidden, self.up_weight, None, raw, rows=n)
+            ops.unary_rows(raw, inner, activation="xielu", rows=n, bias=self.up_bias,
+                           numbers=self.numbers)
+        else:
+            ops.linear(hidden, self.up_weight, self.up_bias, inner, activation=self.activation,
+                       rows=n)
+        ops.linear(inner, self.down_weight, self.down_bias, out, residual=accumulate, rows=n)
 
     def native_part(self, norm: Part, workspace: Workspace):  # noqa: ANN201
         """This feed-forward with ``norm`` in front of it as the C++ host code takes it
         (packed once per workspace)."""
+        if self.learned_unit:  # (the C++ host path knows the built-in units only)
+            return None
         key = (id(norm), id(workspace))
         found = self._native.get(key)
         if found is None:
@@ -82,6 +107,11 @@ class DenseMLP(FeedForward):
         return found
 
     def forward_normed(self, norm: Part, residual: torch.Tensor, step: StepContext) -> None:
+        if self.learned_unit:
+            scratch = step.workspace.buffer("block.normed", self.width, self.ctx.dtype)
+            norm.forward(residual, scratch, count=step.num_rows)  # type: ignore[attr-defined]
+            self.forward(scratch, residual, step)
+            return
         if ops.NATIVE_STEP:
             from ayaka_b200.kernels import native
 

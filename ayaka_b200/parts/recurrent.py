@@ -1,5 +1,6 @@
 """Mixers that carry a fixed-size state per request instead of cached keys: a Mamba-2
-state-space layer, an mLSTM matrix memory and a gated linear attention. The state lives in float32 in the request's
+state-space layer, an mLSTM matrix memory, a gated linear attention and a generalised delta
+rule. The state lives in float32 in the request's
 slot of the cache storage's state tensor, starts at zero, and is carried through whatever
 rows a step brings: ``csrc/recurrent.cu``."""
 
@@ -13,7 +14,7 @@ from ayaka_b200.parts.context import LayerCache, StepContext
 from ayaka_b200.parts.mixer import Mixer
 from ayaka_b200.parts.spec import PartSpec
 
-__all__ = ["MLSTM", "GatedLinearAttention", "Mamba2"]
+__all__ = ["MLSTM", "DeltaRule", "GatedLinearAttention", "Mamba2"]
 
 
 @register_part("mixer", "mamba2")
@@ -231,4 +232,87 @@ class GatedLinearAttention(Mixer):
         # a head is a group of the norm; the weight's `columns` entries repeat for every head
         ops.rms_norm(answer, self.norm_weight, self.eps, gated, groups=heads, count=n,
                      gate=proj[:, 2 * self.qk + self.inner:], gate_mode="silu_after")
+        ops.linear(gated, self.out_weight, None, out, residual=accumulate, rows=n)
+
+
+@register_part("mixer", "delta_rule")
+class DeltaRule(Mixer):
+    """Matrix memory that forgets per key channel and removes along the key before it writes
+    (a generalised delta rule).
+
+    One fused projection gives the receptance ``r``, the key ``k`` and the raw removal rate
+    (``heads x dim`` each), the value ``v`` and an output gate (``heads x columns`` each) and
+    the low-rank input of the decay; ``z = W_up tanh(W_down h) + b`` (``heads x dim``) is the
+    raw decay. Per head, with the unit key ``u = k / sqrt(k . k + 1e-6)``,
+    ``w = exp(-decay_rate * sigmoid(z))`` and ``a = sigmoid(rate + rate_bias)``:
+    ``S <- diag(w) S - (a * u)(u^T S) + k v^T`` (both terms read the old ``S``),
+    ``out = S^T r``. Each head's ``out`` is divided by its root mean square; the joined heads
+    are multiplied by a weight per entry and by ``sigmoid(gate)`` and projected back. Decays,
+    rates, unit keys and the state are float32.
+
+    State of a request: ``S`` per head, ``[heads][columns][dim]``.
+
+    Spec parameters: ``width``, ``num_heads``, ``dim``, ``columns`` (``dim`` when absent),
+    ``decay_rank``, ``decay_rate``, ``eps``.
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext, position: Part | None = None) -> None:
+        super().__init__(ctx)
+        self.width = int(spec.width)  # type: ignore[arg-type]
+        self.num_heads = heads = int(spec.num_heads)  # type: ignore[arg-type]
+        self.dim = int(spec.dim)  # type: ignore[arg-type]
+        self.columns = int(spec.get("columns", self.dim))  # type: ignore[arg-type]
+        self.decay_rank = int(spec.decay_rank)  # type: ignore[arg-type]
+        self.decay_rate = float(spec.decay_rate)  # type: ignore[arg-type]
+        self.eps = float(spec.eps)  # type: ignore[arg-type]
+        if not 1 <= self.dim <= 512 or self.columns < 1 or heads < 1 or self.decay_rank < 1 \
+                or not self.decay_rate >= 0:
+            raise ValueError("the delta rule takes dim in [1, 512], columns, heads and "
+                             "decay_rank >= 1 and a decay_rate >= 0")
+        self.qk = heads * self.dim
+        self.inner = heads * self.columns
+        # r, k, raw rate | v, gate | the decay's low-rank input: one product
+        self.k_at, self.a_at = self.qk, 2 * self.qk
+        self.v_at, self.g_at = 3 * self.qk, 3 * self.qk + self.inner
+        self.low_at = 3 * self.qk + 2 * self.inner
+        self.proj_weight = self.add_param("proj.weight", (self.low_at + self.decay_rank,
+                                                          self.width), "matrix")
+        self.rate_bias = self.add_param("rate.bias", (self.qk,), "vector")
+        self.decay_up = self.add_param("decay_up.weight", (self.qk, self.decay_rank), "matrix")
+        self.decay_bias = self.add_param("decay_up.bias", (self.qk,), "vector")
+        self.norm_weight = self.add_param("norm.weight", (self.inner,), "vector")
+        self.out_weight = self.add_param("out.weight", (self.width, self.inner), "matrix")
+
+    def state_need(self) -> StateNeed:
+        return StateNeed((self.num_heads * self.dim * self.columns,))
+
+    def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext,
+                cache: LayerCache) -> None:
+        self._run(hidden, residual, step, cache, accumulate=True)
+
+    def forward_into(self, hidden: torch.Tensor, out: torch.Tensor, step: StepContext,
+                     cache: LayerCache) -> None:
+        """The same, written into ``out`` (fp32 ``[N, width]``) instead of added to it."""
+        self._run(hidden, out, step, cache, accumulate=False)
+
+    def _run(self, hidden: torch.Tensor, out: torch.Tensor, step: StepContext,
+             cache: LayerCache, accumulate: bool) -> None:
+        n, work, heads = step.num_rows, step.workspace, self.num_heads
+        state = cache.state
+        assert state is not None
+        proj = work.buffer("delta.proj", self.proj_weight.shape[0], torch.float32)
+        low = work.buffer("delta.low", self.decay_rank, self.ctx.dtype)
+        decay = work.buffer("delta.decay", self.qk, torch.float32)
+        answer = work.buffer("delta.answer", self.inner, torch.float32)
+        gated = work.buffer("delta.gated", self.inner, self.ctx.dtype)
+        ops.linear(hidden, self.proj_weight, None, proj, rows=n)
+        ops.unary_rows(proj[:, self.low_at:], low, activation="tanh", rows=n)
+        ops.linear(low, self.decay_up, self.decay_bias, decay, rows=n)
+        ops.delta_scan(proj, decay, self.rate_bias, state, answer, row_start=step.row_start,
+                       state_slot=step.state_slot, requests=step.num_requests, heads=heads,
+                       dim=self.dim, columns=self.columns, k_offset=self.k_at,
+                       v_offset=self.v_at, a_offset=self.a_at, decay_rate=self.decay_rate)
+        # a head is a group of the norm: each divided by its own root mean square
+        ops.rms_norm(answer, self.norm_weight, self.eps, gated, groups=heads, count=n,
+                     gate=proj[:, self.g_at:self.g_at + self.inner], gate_mode="sigmoid_after")
         ops.linear(gated, self.out_weight, None, out, residual=accumulate, rows=n)
