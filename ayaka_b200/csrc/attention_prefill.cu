@@ -20,6 +20,12 @@
 // `gate` (fp32, one raw gate per output entry: the result is multiplied by its sigmoid).
 // When the value pages are the key pages themselves (attention over latent rows) the kernel's
 // other instantiation fetches one tile per block of keys and uses it in both products.
+// `pool` (with a window, without kept keys): behind the window a row at position p also sees
+// one pooled key and value for each block of `pool` positions e with e * pool + pool - 1 <=
+// p - window; the pooled rows lie beside the pages ([page][kv head][pool_slots][dim], block e
+// in the page of its first position, at slot (e * pool % page_size) / pool) and are walked
+// first, 64 at a time, then the window's keys. `sink` (one float per head): the softmax's
+// denominator also holds exp(sink[head]).
 //
 // This kernel uses the legacy warp-level tensor path (not tcgen05): attention is ~5% of a
 // prefill step's FLOPs and this dataflow is proven; the matrix products that dominate run on
@@ -115,6 +121,29 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* tile,
   }
 }
 
+// Gather 64 pooled rows (entries entry0 .. of the `entries` the tile can see) into a shared tile.
+template <int D>
+__device__ __forceinline__ void load_pool_block(__nv_bfloat16* tile,
+                                                const __nv_bfloat16* __restrict__ rows,
+                                                const int* __restrict__ table, int entry0,
+                                                int entries, int pool, int pool_slots,
+                                                int num_kv_heads, int kv_head, int page_size) {
+  constexpr int CHUNKS = D / 8, STRIDE = D + 8;
+  for (int i = threadIdx.x; i < PF_BN * CHUNKS; i += 128) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    const int entry = entry0 + r;
+    const bool valid = entry < entries;
+    const __nv_bfloat16* src = rows;
+    if (valid) {
+      const int first = entry * pool;
+      const int page = table[first / page_size];
+      src = rows + (((size_t)page * num_kv_heads + kv_head) * pool_slots +
+                    (first % page_size) / pool) * D + c * 8;
+    }
+    cp_async16(tile + r * STRIDE + c * 8, src, valid);
+  }
+}
+
 template <bool SAME>  // the value pages are the key pages: one tile serves both products
 __global__ void __launch_bounds__(128)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
@@ -125,7 +154,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
                          __nv_bfloat16* __restrict__ out, int ld_out, int num_requests,
                          int num_kv_heads, int group, int page_size, float scale, int window,
                          int total_tiles, int page_shift, int keep_first,
-                         const float* __restrict__ gate, int ld_gate) {
+                         const float* __restrict__ gate, int ld_gate, int pool, int pool_slots,
+                         const __nv_bfloat16* __restrict__ k_pool,
+                         const __nv_bfloat16* __restrict__ v_pool,
+                         const float* __restrict__ sink) {
   extern __shared__ __align__(16) unsigned char pf_smem[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(pf_smem);
   __nv_bfloat16* k_s = q_s + PF_QTILE;      // two stages
@@ -135,7 +167,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   __nv_bfloat16* v_s = same ? k_s : k_s + 2 * PF_TILE;  // two stages
 
   pdl_launch_dependents();
-  pdl_wait_for(q, k_pages, v_pages, gate);
+  pdl_wait_for(q, k_pages, v_pages, gate, k_pool, v_pool);
   // Which request and which 64-row tile of it. Heads run along grid.x and tiles along grid.y
   // from the last tile down: a tile's work grows with its position in the sequence, and the
   // longest tiles must start first or they finish alone at the end.
@@ -170,9 +202,33 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   const int kept = (window > 0 && keep_first < lo_min) ? keep_first : (window > 0 ? lo_min : 0);
   int kept_blocks = (kept + PF_BN - 1) / PF_BN;
   if (kept_blocks > block_lo) kept_blocks = block_lo;
+  // pooled rows the tile's last row sees: they take the place of the kept keys' blocks
+  const bool pooled = !SAME && pool > 0 && window > 0;
+  const int pool_entries = (pooled && last_key - window + 1 > 0) ? (last_key - window + 1) / pool
+                                                                 : 0;
+  if (pooled) kept_blocks = (pool_entries + PF_BN - 1) / PF_BN;
   const int turns = kept_blocks + block_hi - block_lo + 1;
-  const int keep = window > 0 ? keep_first : 0;
+  const int keep = (window > 0 && !pooled) ? keep_first : 0;
   const int* table = block_table + (size_t)req * table_stride;
+  // one block of keys and of values into a stage: pooled rows or cached tokens
+  auto load_turn = [&](int turn, int stage) {
+    __nv_bfloat16* k_to = k_s + stage * PF_TILE;
+    __nv_bfloat16* v_to = v_s + stage * PF_VTILE;
+    if (pooled && turn < kept_blocks) {
+      load_pool_block<PF_HD>(k_to, k_pool, table, turn * PF_BN, pool_entries, pool, pool_slots,
+                             num_kv_heads, kv_head, page_size);
+      load_pool_block<PF_VD>(v_to, v_pool, table, turn * PF_BN, pool_entries, pool, pool_slots,
+                             num_kv_heads, kv_head, page_size);
+      return;
+    }
+    const int block = turn < kept_blocks ? turn : block_lo + (turn - kept_blocks);
+    load_kv_block<PF_HD>(k_to, k_pages, table, block * PF_BN, lo_min, last_key, keep,
+                         num_kv_heads, kv_head, page_size, page_shift);
+    if (!same) {
+      load_kv_block<PF_VD>(v_to, v_pages, table, block * PF_BN, lo_min, last_key, keep,
+                           num_kv_heads, kv_head, page_size, page_shift);
+    }
+  };
 
   // Q tile and the first K/V block
   for (int i = threadIdx.x; i < PF_BM * PF_CHUNKS; i += 128) {
@@ -182,13 +238,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
         q + (size_t)(first_row + (valid ? r : 0)) * ld_q + head * PF_HD + c * 8;
     cp_async16(q_s + r * PF_STRIDE + c * 8, src, valid);
   }
-  const int block0 = kept_blocks > 0 ? 0 : block_lo;
-  load_kv_block<PF_HD>(k_s, k_pages, table, block0 * PF_BN, lo_min, last_key, keep,
-                       num_kv_heads, kv_head, page_size, page_shift);
-  if (!same) {
-    load_kv_block<PF_VD>(v_s, v_pages, table, block0 * PF_BN, lo_min, last_key, keep,
-                         num_kv_heads, kv_head, page_size, page_shift);
-  }
+  load_turn(0, 0);
   cp_async_commit();
 
   float o[PF_VD / 8][4];
@@ -204,13 +254,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     const int block = turn < kept_blocks ? turn : block_lo + (turn - kept_blocks);
     const int stage = turn & 1;
     if (turn + 1 < turns) {  // prefetch the next block into the other stage
-      const int next = turn + 1 < kept_blocks ? turn + 1 : block_lo + (turn + 1 - kept_blocks);
-      load_kv_block<PF_HD>(k_s + (stage ^ 1) * PF_TILE, k_pages, table, next * PF_BN, lo_min,
-                           last_key, keep, num_kv_heads, kv_head, page_size, page_shift);
-      if (!same) {
-        load_kv_block<PF_VD>(v_s + (stage ^ 1) * PF_VTILE, v_pages, table, next * PF_BN, lo_min,
-                             last_key, keep, num_kv_heads, kv_head, page_size, page_shift);
-      }
+      load_turn(turn + 1, stage ^ 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -250,7 +294,25 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     const int key_base = block * PF_BN + (lane & 3) * 2;
     const bool all_seen = window == 0 && block * PF_BN + PF_BN - 1 <= pos0 + warp * 16;
     float block_max[2] = {-INFINITY, -INFINITY};
-    if (all_seen) {
+    if (pooled && turn < kept_blocks) {
+      // a turn of pooled rows: entry e is seen by the row at position p when
+      // e < (p - window + 1) / pool
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int behind = row_a + h * 8 - window + 1;
+        const int seen_entries = behind > 0 ? behind / pool : 0;
+#pragma unroll
+        for (int t = 0; t < PF_BN / 8; ++t) {
+#pragma unroll
+          for (int e = 2 * h; e < 2 * h + 2; ++e) {
+            const int entry = key_base + t * 8 + (e & 1);
+            const float v = entry < seen_entries ? s[t][e] * scale2 : -INFINITY;
+            s[t][e] = v;
+            block_max[h] = fmaxf(block_max[h], v);
+          }
+        }
+      }
+    } else if (all_seen) {
 #pragma unroll
       for (int t = 0; t < PF_BN / 8; ++t) {
 #pragma unroll
@@ -329,7 +391,19 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     run_sum[h] += __shfl_xor_sync(0xffffffffu, run_sum[h], 1);
     run_sum[h] += __shfl_xor_sync(0xffffffffu, run_sum[h], 2);
   }
-  const float inv0 = 1.f / run_sum[0], inv1 = 1.f / run_sum[1];
+  float inv0 = 1.f / run_sum[0], inv1 = 1.f / run_sum[1];
+  if (sink != nullptr) {  // one more entry of the denominator, without a value
+    const float sink2 = sink[head] * 1.4426950408889634f;
+    float inv[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float new_max = fmaxf(run_max[h], sink2);
+      const float corr = exp2f(run_max[h] - new_max);
+      inv[h] = corr / (run_sum[h] * corr + exp2f(sink2 - new_max));
+    }
+    inv0 = inv[0];
+    inv1 = inv[1];
+  }
   const int r0 = warp * 16 + (lane >> 2);
   const float* gate_a = nullptr;  // the raw gates of this thread's two rows
   const float* gate_b = nullptr;
@@ -371,17 +445,25 @@ AYK_API int ayk_attention_prefill_value_dim() { return ayk::PF_VD; }
 // bfloat16 only. q/out rows are 16-byte aligned (ld multiples of 8 elements). `total_tiles`
 // = sum over requests of ceil(rows / 64), computed by the caller from its host copy of the
 // rows.
-AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
-                                  const void* v_pages, const int* block_table, int table_stride,
-                                  const int* row_start, const int* kv_len, void* out, int ld_out,
-                                  int num_requests, int total_tiles, int num_heads,
-                                  int num_kv_heads, int head_dim, int page_size, float scale,
-                                  int window, int value_dim, int keep_first, const float* gate,
-                                  int ld_gate, void* stream) {
+// The same with pooled rows behind the window and a sink (see the head of this file); pool 0
+// and null pointers: none of them.
+AYK_API int ayk_attention_prefill_pooled(
+    const void* q, int ld_q, const void* k_pages, const void* v_pages, const int* block_table,
+    int table_stride, const int* row_start, const int* kv_len, void* out, int ld_out,
+    int num_requests, int total_tiles, int num_heads, int num_kv_heads, int head_dim,
+    int page_size, float scale, int window, int value_dim, int keep_first, const float* gate,
+    int ld_gate, int pool, int pool_slots, const void* k_pool, const void* v_pool,
+    const float* sink, void* stream) {
   using namespace ayk;
   if (num_requests == 0 || total_tiles == 0) return AYK_OK;
   if (head_dim != PF_HD || value_dim != PF_VD || keep_first < 0 ||
       (gate != nullptr && ld_gate < num_heads * PF_VD)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (pool < 0 || (pool > 0 && window > 0 &&
+                   (keep_first != 0 || k_pool == nullptr || v_pool == nullptr ||
+                    v_pages == k_pages || pool_slots != (page_size + pool - 1) / pool ||
+                    ((uintptr_t)k_pool % 16) || ((uintptr_t)v_pool % 16)))) {
     return AYK_BAD_ARGUMENT;
   }
   if (num_requests < 0 || total_tiles < 0 || num_heads < 1 || num_kv_heads < 1 ||
@@ -420,7 +502,8 @@ AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
                            (const __nv_bfloat16*)v_pages, block_table, table_stride, row_start,
                            kv_len, (__nv_bfloat16*)out, ld_out, num_requests, num_kv_heads,
                            num_heads / num_kv_heads, page_size, scale, window, total_tiles,
-                           page_shift, keep_first, gate, ld_gate);
+                           page_shift, keep_first, gate, ld_gate, pool, pool_slots,
+                           (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, sink);
     }
   }
   return launch_kernel(attention_prefill_kernel<false>, dim3(num_heads, total_tiles), dim3(128),
@@ -428,5 +511,20 @@ AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
                        table_stride, row_start, kv_len, (__nv_bfloat16*)out, ld_out, num_requests,
                        num_kv_heads, num_heads / num_kv_heads, page_size, scale, window,
-                       total_tiles, page_shift, keep_first, gate, ld_gate);
+                       total_tiles, page_shift, keep_first, gate, ld_gate, pool, pool_slots,
+                           (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, sink);
+}
+
+AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
+                                  const void* v_pages, const int* block_table, int table_stride,
+                                  const int* row_start, const int* kv_len, void* out, int ld_out,
+                                  int num_requests, int total_tiles, int num_heads,
+                                  int num_kv_heads, int head_dim, int page_size, float scale,
+                                  int window, int value_dim, int keep_first, const float* gate,
+                                  int ld_gate, void* stream) {
+  return ayk_attention_prefill_pooled(q, ld_q, k_pages, v_pages, block_table, table_stride,
+                                      row_start, kv_len, out, ld_out, num_requests, total_tiles,
+                                      num_heads, num_kv_heads, head_dim, page_size, scale, window,
+                                      value_dim, keep_first, gate, ld_gate, 0, 0, nullptr,
+                                      nullptr, nullptr, stream);
 }

@@ -92,7 +92,7 @@ NATIVE_STEP = True
 #: How :class:`~ayaka_b200.parts.pooled_attention.PooledWindowAttention` runs bfloat16 prompt
 #: portions: ``"mma"`` (the flash kernel on the tensor cores) or ``"generic"`` (one CTA per
 #: row and head on the CUDA cores); tests switch it to compare the two.
-POOLED_PREFILL = "generic"
+POOLED_PREFILL = "mma"
 
 _launches = 0
 
@@ -466,7 +466,9 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       block_table: torch.Tensor, row_start: torch.Tensor, kv_len: torch.Tensor,
                       out: torch.Tensor, *, num_heads: int, scale: float, host_rows: list[int],
                       window: int = 0, kernel: str | None = None, keep_first: int = 0,
-                      gate: torch.Tensor | None = None) -> None:
+                      gate: torch.Tensor | None = None, pool: int = 0,
+                      k_pool: torch.Tensor | None = None, v_pool: torch.Tensor | None = None,
+                      sink: torch.Tensor | None = None) -> None:
     """Causal attention of prompt portions in bfloat16 on the tensor cores.
 
     Request ``b`` owns rows ``row_start[b] .. row_start[b + 1]`` of ``q`` and ``out``, which
@@ -475,7 +477,10 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     sizes on a warp-level kernel compiled for the head size (``kernel`` forces one of them).
     The warp-level kernel also takes value rows of another size than key rows (``v_pages``'
     last dimension), ``keep_first`` (with a window: keys before that position stay visible)
-    and ``gate`` (float32 ``[N, num_heads * value size]``: the result times its sigmoid).
+    and ``gate`` (float32 ``[N, num_heads * value size]``: the result times its sigmoid);
+    with ``pool`` and a window the pooled rows ``k_pool`` / ``v_pool`` of the blocks that lie
+    wholly behind a row's window (see :func:`pooled_attention`), and with ``sink`` (float32
+    ``[num_heads]``) one more entry ``exp(sink[head])`` in the softmax's denominator.
     """
     op = "attention_prefill"
     if _left_out and op in _left_out:
@@ -503,7 +508,21 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         _need(op, "gate", gate, torch.float32, 2)
         if gate.shape[1] != num_heads * value_dim or gate.stride(1) != 1:
             raise BackendError(f"{op}: the gate does not match the output")
-    plain = value_dim == head_dim and gate is None and not (keep_first and window)
+    pooled = bool(pool and window)
+    if pooled:
+        _need(op, "k_pool", k_pool, torch.bfloat16, 4)
+        _need(op, "v_pool", v_pool, torch.bfloat16, 4)
+        slots = pool_slots(page_size, pool)
+        if tuple(k_pool.shape) != (k_pages.shape[0], kv_heads, slots, head_dim) or \
+                tuple(v_pool.shape) != (k_pages.shape[0], kv_heads, slots, value_dim) or \
+                not k_pool.is_contiguous() or not v_pool.is_contiguous() or keep_first:
+            raise BackendError(f"{op}: the pooled rows do not match the pages")
+    if sink is not None:
+        _need(op, "sink", sink, torch.float32, 1)
+        if sink.shape[0] != num_heads:
+            raise BackendError(f"{op}: one sink per head")
+    plain = value_dim == head_dim and gate is None and not (keep_first and window) and \
+        not pooled and sink is None
     # the tcgen05 kernel works on tiles of 256 rows: a step of short portions only is better
     # served by the warp-level kernel's tiles of 64
     which = kernel or (PREFILL_ATTENTION if head_dim == 64 and scale > 0 and plain
@@ -527,13 +546,16 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     sizes = {"AYK_HEAD_DIM": head_dim}
     if value_dim != head_dim:
         sizes["AYK_VALUE_DIM"] = value_dim
-    fn = library("attention_prefill", **sizes).ayk_attention_prefill
+    fn = library("attention_prefill", **sizes).ayk_attention_prefill_pooled
     status = fn(_ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                 c_int(block_table.stride(0)), _ptr(row_start), _ptr(kv_len), _ptr(out),
                 c_int(out.stride(0)), c_int(count), c_int(tiles), c_int(num_heads),
                 c_int(kv_heads), c_int(head_dim), c_int(page_size), c_float(scale),
                 c_int(window), c_int(value_dim), c_int(keep_first), _ptr(gate),
-                c_int(0 if gate is None else gate.stride(0)), _stream())
+                c_int(0 if gate is None else gate.stride(0)),
+                c_int(pool if pooled else 0), c_int(pool_slots(page_size, pool) if pooled else 0),
+                _ptr(k_pool if pooled else None), _ptr(v_pool if pooled else None), _ptr(sink),
+                _stream())
     check(status, op)
 
 
