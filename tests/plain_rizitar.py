@@ -106,8 +106,8 @@ def attention(h: np.ndarray, t: dict, prefix: str, mixer: dict, eps: float) -> n
     size, pool = int(mask.get("size") or 0), int(mask.get("pool") or 0)
     tokens, blocks = pooled_mask(count, size, pool)
     nblocks = blocks.shape[1]
-    kb = k[:nblocks * pool].reshape(nblocks, pool, kv_heads, dim).mean(axis=1)
-    vb = v[:nblocks * pool].reshape(nblocks, pool, kv_heads, vdim).mean(axis=1)
+    kb = k[:nblocks * pool].reshape(nblocks, max(pool, 1), kv_heads, dim).sum(axis=1) / max(pool, 1)
+    vb = v[:nblocks * pool].reshape(nblocks, max(pool, 1), kv_heads, vdim).sum(axis=1) / max(pool, 1)
     scale = float(mixer["scale"])
     sink = t.get(prefix + "sink")
     out = np.zeros((count, heads, vdim))
