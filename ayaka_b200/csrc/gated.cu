@@ -14,6 +14,15 @@ namespace ayk {
 
 enum GateAct : int { GATE_SILU = 0, GATE_GELU_TANH = 1 };
 
+// The tanh GELU 0.5 z (1 + tanh(t)), t = sqrt(2 / pi) (z + 0.044715 z^3), written as
+// z / (1 + exp(-2 t)): the same function without the sum 1 + tanh(t), which for negative z
+// cancels to a few digits in fp32. A gate is a factor: where all gates of a row are small,
+// what follows (a norm over the gated row's projection) keeps their relative error.
+__device__ __forceinline__ float gelu_tanh_ratio(float z) {
+  const float t = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return z / (1.f + expf(-2.f * t));
+}
+
 template <typename T>
 __global__ void cast_rows_kernel(const float* __restrict__ x, int ld_x, T* __restrict__ out,
                                  int ld_out, int rows, int width) {
@@ -40,7 +49,7 @@ __global__ void gated_unit_kernel(const float* __restrict__ gate, int ld_gate,
        i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / width), c = (int)(i % width);
     const float g = gate[(size_t)r * ld_gate + c];
-    const float a = act == GATE_GELU_TANH ? gelu_tanh(g) : g / (1.f + expf(-g));
+    const float a = act == GATE_GELU_TANH ? gelu_tanh_ratio(g) : g / (1.f + expf(-g));
     float b = 0.f;
     if (other != nullptr) {
       b = other[(size_t)r * ld_other + c];

@@ -22,7 +22,8 @@ workloads of BASELINE.json's other configurations (see :func:`workload_run`);
 ``--workload small|large`` runs one of them alone and prints a line of its own;
 ``--design mapuvik`` runs that design beside GPT-2 of equal size, ``--design gagotar`` that
 design beside Mapuvik and GPT-2, ``--design semadra`` that design beside Gagotar, Mapuvik and
-GPT-2 (``bench_design.py``).
+GPT-2, ``--design rizitar`` that design beside Semadra, Gagotar and GPT-2
+(``bench_design.py``).
 """
 
 from __future__ import annotations
@@ -519,7 +520,7 @@ def main() -> int:
                         help="instead of the headline run: one of the two serving workloads "
                              "(GPT-2 small with 64 ragged requests; GPT-2 large with prompt "
                              "portions beside 32 decoding requests)")
-    parser.add_argument("--design", choices=("mapuvik", "gagotar", "semadra"),
+    parser.add_argument("--design", choices=("mapuvik", "gagotar", "semadra", "rizitar"),
                         help="instead of the headline run: the named design beside GPT-2 (and, "
                              "for gagotar, Mapuvik; for semadra, Gagotar and Mapuvik) of equal "
                              "size, prompt step and decode step "

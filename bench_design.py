@@ -1,8 +1,10 @@
-"""``bench.py --design mapuvik`` / ``gagotar`` / ``semadra``: prefill and decode throughput of
-the design at sizes that resemble a real model's layers, beside GPT-2 of the same width, heads,
-feed-forward and number of layers (Gagotar also beside Mapuvik, the design whose kernels are
-closest to its own; Semadra beside Gagotar, whose experts and attention, and Mapuvik, whose
-latent attention are the like kernels), on one B200 with random bf16 weights.
+"""``bench.py --design mapuvik`` / ``gagotar`` / ``semadra`` / ``rizitar``: prefill and decode
+throughput of the design at sizes that resemble a real model's layers, beside GPT-2 of the same
+width, heads, feed-forward and number of layers (Gagotar also beside Mapuvik, the design whose
+kernels are closest to its own; Semadra beside Gagotar, whose experts and attention, and
+Mapuvik, whose latent attention are the like kernels; Rizitar beside Semadra, whose windowed
+attention, norms behind the sublayers, experts and token input, and Gagotar, whose scan over a
+matrix state are the like kernels), on one B200 with random bf16 weights.
 
 For each size and model: one prompt step of 2,048 tokens (two prompts of 1,024) and one decode
 step of 8 requests at context 1,025, each timed on the device as a CUDA-graph replay of the
@@ -92,6 +94,33 @@ def semadra_config(width: int, heads: int, ff: int, repeats: int, vocab: int) ->
     return {"architecture": "Semadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "embedding": {"scale": width ** 0.5}, "residual_mult": 0.5,
             "token_side": {"dim": 64}, "layers": layers}
+
+
+#: Rizitar at the bench's sizes: windows of 512 positions behind which blocks of 16 are pooled
+#: (the decode step at context 1,025 sees 512 keys and 32 pooled rows), heads wholly rotated
+#: with blended frequencies; delta layers with heads of 64 channels; a dense feed-forward in
+#: the first layer of three, experts as in Gagotar's configuration in the other two
+RIZITAR_WINDOW, RIZITAR_POOL, RIZITAR_EXPERTS, RIZITAR_TOP = 512, 16, 16, 2
+
+
+def rizitar_config(width: int, heads: int, ff: int, repeats: int, vocab: int) -> dict:
+    head = width // heads
+    attention = {"heads": heads, "kv_heads": heads // 4, "dim": head, "vdim": head,
+                 "scale": head ** -0.5, "mask": {"size": RIZITAR_WINDOW, "pool": RIZITAR_POOL},
+                 "rot": {"base": 10000.0, "dims": head,
+                         "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0,
+                                     "slow": 1.0}}}
+    memory = {"heads": width // 64, "dim": 64, "decay_rank": 64}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4},
+           "router": {"experts": RIZITAR_EXPERTS, "top": RIZITAR_TOP}}
+    layers = []
+    for _ in range(repeats):
+        layers += [
+            {"type": "attention", "mixer": attention, "mlp": {"kind": "dense", "ff": ff}},
+            {"type": "attention", "mixer": attention, "mlp": moe},
+            {"type": "general_delta", "mixer": memory, "mlp": moe}]
+    return {"architecture": "Rizitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": width ** 0.5}, "token_side": {"dim": 64}, "layers": layers}
 
 
 def gpt2_config(width: int, heads: int, ff: int, layers: int, vocab: int) -> dict:
@@ -187,6 +216,64 @@ def _class_work(config: dict, rows: int, keys_per_row: float, decode: bool,
             add("moe_experts", 2.0 * rows * top * 3 * f * width,
                 min(E, rows * top) * 3 * f * width * 2 + rows * top * (width * 6 + f * 4))
             add("moe_join", 0.0, rows * width * (4 * top + 8))
+        product(config["vocab"], width, 4, wanted)
+        return work
+    if config["architecture"] == "Rizitar":
+        side = (config.get("token_side") or {}).get("dim", 0)
+        for layer in config["layers"]:
+            m, mlp = layer["mixer"], layer["mlp"]
+            add("rms_norm", 0.0, rows * width * 6)
+            if layer["type"] == "attention":
+                H, G, dim = m["heads"], m.get("kv_heads", m["heads"]), m["dim"]
+                window = (m.get("mask") or {}).get("size", 0)
+                pool = (m.get("mask") or {}).get("pool", 0)
+
+                def seen(p: int) -> int:  # keys and pooled rows the row at position p attends
+                    if not window or p < window:
+                        return p + 1
+                    return window + ((p - window + 1) // pool if pool else 0)
+
+                keys = seen(int(keys_per_row) - 1) if decode else \
+                    sum(seen(p) for p in range(LENGTH)) / LENGTH
+                reuse = 1 if decode else 64 / 8  # a tile of 64 rows shares its keys
+                product(H * dim + G * dim, width, 4)
+                add("pooled_prepare", 0.0, rows * (H * dim + G * dim) * 4
+                    + rows * (H * dim + 2 * G * dim) * 2)
+                if pool:
+                    add("pooled_blocks", 0.0, rows * G * 2 * dim * 2 * (1 + 1 / pool))
+                add("pooled_attention", 4.0 * rows * keys * H * dim,
+                    rows * keys * G * 2 * dim * 2 / reuse + rows * H * dim * 4)
+                product(width, H * dim, 4)
+            else:
+                H, N, rank = m["heads"], m["dim"], m["decay_rank"]
+                product(5 * H * N + rank, width, 4)
+                add("unary_rows", 0.0, rows * rank * 6)
+                product(H * N, rank, 4)
+                add("delta_scan", 8.0 * rows * H * N * N,
+                    rows * 6 * H * N * 4 + (2 * H * N * N * 4) * (rows if decode else PROMPTS))
+                add("rms_norm", 0.0, rows * H * N * 10)
+                product(width, H * N, 4)
+            add("norm_add", 0.0, rows * width * 14)
+            if mlp is not None:
+                add("rms_norm", 0.0, rows * width * 6)
+                if mlp["kind"] == "dense":
+                    product(mlp["ff"], width, 4)
+                    add("unary_rows", 0.0, rows * mlp["ff"] * 6)
+                    product(width, mlp["ff"], 4)
+                else:
+                    E, top, f = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+                    product(E, width, 4)
+                    add("moe_route", 0.0, rows * (E + 2 * top) * 4)
+                    add("moe_experts", 2.0 * rows * top * 2 * f * width,
+                        min(E, rows * top) * 2 * f * width * 2 + rows * top * (width * 6 + f * 4))
+                    add("moe_join", 0.0, rows * width * (4 * top + 4))
+                add("norm_add", 0.0, rows * width * 14)
+            if side:
+                product(side, width, 4)
+                add("gated_unit", 0.0, rows * side * 8)
+                product(width, side, 4)
+                add("norm_add", 0.0, rows * width * 14)
+        add("rms_norm", 0.0, wanted * width * 6)
         product(config["vocab"], width, 4, wanted)
         return work
     if config["architecture"] == "Semadra":
@@ -369,7 +456,8 @@ def _measure(config: dict, peak: dict) -> dict:
             for klass, pairs in record.items():
                 name = klass
                 if klass == "attention_prefill":
-                    name = "latent_attention" if "latent_attention" in work else "attention"
+                    name = "pooled_attention" if "pooled_attention" in work else (
+                        "latent_attention" if "latent_attention" in work else "attention")
                 elif klass == "latent_decode":
                     name = "latent_attention"
                 if name in work:
@@ -437,16 +525,21 @@ def run(sizes: str | None = None, design: str = "mapuvik") -> dict:
     for name in picked:
         width, heads, ff, repeats = table[name]
         results[name] = {"layers": 3 * repeats, "width": width, "heads": heads, "ff": ff}
-        if design == "semadra":
+        if design == "rizitar":
+            results[name]["rizitar"] = _measure(
+                rizitar_config(width, heads, ff, repeats, 32000), peak)
+        if design in ("semadra", "rizitar"):
             results[name]["semadra"] = _measure(
                 semadra_config(width, heads, ff, repeats, 32000), peak)
-        if design in ("gagotar", "semadra"):
+        if design in ("gagotar", "semadra", "rizitar"):
             results[name]["gagotar"] = _measure(
                 gagotar_config(width, heads, ff, 3 * repeats, 32000), peak)
-        results[name]["mapuvik"] = _measure(mapuvik_config(width, heads, ff, repeats, 32000),
-                                            peak)
+        if design != "rizitar":
+            results[name]["mapuvik"] = _measure(
+                mapuvik_config(width, heads, ff, repeats, 32000), peak)
         results[name]["gpt2"] = _measure(gpt2_config(width, heads, ff, 3 * repeats, 32000), peak)
-    title = {"gagotar": "Gagotar beside Mapuvik and GPT-2",
+    title = {"rizitar": "Rizitar beside Semadra, Gagotar and GPT-2",
+             "gagotar": "Gagotar beside Mapuvik and GPT-2",
              "semadra": "Semadra beside Gagotar, Mapuvik and GPT-2"}.get(
                  design, "Mapuvik beside GPT-2")
     return {"metric": f"{title} of equal size: one 2,048-token prompt step and one "

@@ -55,10 +55,11 @@ def draw_model(rng: random.Random) -> dict:
         layers.append(layer(entry, draw_mlp(rng)))
     return model(rng.choice([17, 64, 101, 300]), width, rng.choice([1e-5, 1e-6, 1e-3]), layers,
                  embed_scale=rng.choice([None, 1.0, 3.0, 12.0]),
-                 # (a token input of one entry is left out: its branch is one vector times one
-                 # gate, and the norm behind it blows a gate near zero up to full size, so that
-                 # the plain model itself moves by 1e-4 under weight noise of 1e-7)
-                 side=rng.choice([None, 2, 4, 10]))
+                 # (a token input of one or two entries is left out: its branch is one or two
+                 # vectors times as many gates, and the norm behind it blows gates near zero up
+                 # to full size, so that the plain model itself moves by 1e-4 under weight
+                 # noise of 1e-7)
+                 side=rng.choice([None, 3, 4, 10]))
 
 
 def draw_steps(rng: random.Random, sequences: dict[str, list[int]], pool_tokens: int
