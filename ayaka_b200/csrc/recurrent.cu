@@ -569,18 +569,17 @@ delta_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
     float* v_s = au_s + (size_t)chunk * N;
     float* inv_s = v_s + (size_t)chunk * SCAN_COLS;  // 1 / length of each row's key
     const int t0 = c * chunk, count = min(chunk, rows - t0);
-    for (int i = warp; i < count; i += warps) {  // a warp per row: the key's length
-      float ss = 0.f;
+    for (int i = warp; i < count; i += warps) {  // a warp per row: the key's length, then
+      float ss = 0.f;                            // the row's factors
       for (int n = lane; n < N; n += 32) ss = fmaf(k_s[i * N + n], k_s[i * N + n], ss);
-      ss = group_sum<32>(ss);
-      if (lane == 0) inv_s[i] = 1.f / sqrtf(ss + 1e-6f);
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < count * N; i += blockDim.x) {
-      const int n = i % N;
-      w_s[i] = expf(-decay_rate / (1.f + expf(-w_s[i])));
-      const float rate = 1.f / (1.f + expf(-(au_s[i] + a_bias[h * N + n])));
-      au_s[i] = rate * k_s[i] * inv_s[i / N];
+      const float inv = 1.f / sqrtf(group_sum<32>(ss) + 1e-6f);
+      if (lane == 0) inv_s[i] = inv;
+      for (int n = lane; n < N; n += 32) {
+        const int at = i * N + n;
+        w_s[at] = expf(-decay_rate / (1.f + expf(-w_s[at])));
+        const float rate = 1.f / (1.f + expf(-(au_s[at] + a_bias[h * N + n])));
+        au_s[at] = rate * k_s[at] * inv;
+      }
     }
     __syncthreads();
 #pragma unroll 2
