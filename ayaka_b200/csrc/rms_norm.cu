@@ -158,11 +158,16 @@ __global__ void norm_sum_kernel(Branches in, int count, float eps, float factor,
 // dst[r][c] += factor * x[r][c] * rsqrt(mean_c(x[r]^2) + eps) * (offset + w[c]), and, when
 // `copy` is given, copy[r][c] = the new dst[r][c] in the compute type: a sublayer's normed
 // result joins the fp32 residual stream and the next sublayer's input leaves the same pass.
+// When `next_out` is given, also next_out[r][c] = v[c] * rsqrt(mean_c(v^2) + next_eps) *
+// (next_offset + next_weight[c]) with v the new dst[r]: the norm in front of the next sublayer,
+// from the row that is in registers anyway (one more sum over the row, no launch of its own).
 template <typename TOut>
 __global__ void norm_add_kernel(const float* __restrict__ x, int ld_x,
                                 const float* __restrict__ weight, float offset, float eps,
                                 float factor, float* __restrict__ dst, int ld_dst,
-                                TOut* __restrict__ copy, int ld_copy, int width) {
+                                TOut* __restrict__ copy, int ld_copy, int width,
+                                const float* __restrict__ next_weight, float next_offset,
+                                float next_eps, TOut* __restrict__ next_out, int ld_next) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   const int r = blockIdx.x;
@@ -190,6 +195,7 @@ __global__ void norm_add_kernel(const float* __restrict__ x, int ld_x,
 #pragma unroll
     for (int i = 0; i < NA_KEEP; ++i) s += xs[i] * xs[i];
     const float inv = factor / sqrtf(block_sum(s, scratch) / (float)width + eps);
+    float s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < NA_KEEP; ++i) {
       const int c = threadIdx.x + i * blockDim.x;
@@ -197,6 +203,18 @@ __global__ void norm_add_kernel(const float* __restrict__ x, int ld_x,
         const float v = ds[i] + xs[i] * inv * ws[i];
         to[c] = v;
         if (copy != nullptr) stf(copy + (size_t)r * ld_copy + c, v);
+        ds[i] = v;
+        s2 += v * v;
+      }
+    }
+    if (next_out != nullptr) {
+      const float inv2 = 1.f / sqrtf(block_sum(s2, scratch) / (float)width + next_eps);
+#pragma unroll
+      for (int i = 0; i < NA_KEEP; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < width) {
+          stf(next_out + (size_t)r * ld_next + c, ds[i] * inv2 * (next_offset + next_weight[c]));
+        }
       }
     }
     return;
@@ -207,10 +225,18 @@ __global__ void norm_add_kernel(const float* __restrict__ x, int ld_x,
   for (int c = threadIdx.x; c < width; c += blockDim.x) s += src[c] * src[c];
   const float inv = factor / sqrtf(block_sum(s, scratch) / (float)width + eps);
   float* to = dst + (size_t)r * ld_dst;
+  float s2 = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float v = to[c] + src[c] * inv * (offset + weight[c]);
     to[c] = v;
     if (copy != nullptr) stf(copy + (size_t)r * ld_copy + c, v);
+    s2 += v * v;
+  }
+  if (next_out != nullptr) {  // (a thread reads back what it wrote itself)
+    const float inv2 = 1.f / sqrtf(block_sum(s2, scratch) / (float)width + next_eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      stf(next_out + (size_t)r * ld_next + c, to[c] * inv2 * (next_offset + next_weight[c]));
+    }
   }
 }
 
@@ -271,24 +297,39 @@ AYK_API int ayk_scale_add(const float* x, int ld_x, const float* scale, float* d
                        (cudaStream_t)stream, 1, x, ld_x, scale, dst, ld_dst, width, accumulate);
 }
 
-// copy_type: 0 = float32, 1 = bfloat16 (ignored when `copy` is null).
-AYK_API int ayk_norm_add(const float* x, int ld_x, const float* weight, float offset, float eps,
-                         float factor, float* dst, int ld_dst, void* copy, int ld_copy,
-                         int copy_type, int n, int width, void* stream) {
+// copy_type: 0 = float32, 1 = bfloat16, of `copy` and of `next_out` (ignored when both are
+// null). `next_out` with `next_weight`: the following norm's output (see norm_add_kernel).
+AYK_API int ayk_norm_add_next(const float* x, int ld_x, const float* weight, float offset,
+                              float eps, float factor, float* dst, int ld_dst, void* copy,
+                              int ld_copy, int copy_type, const float* next_weight,
+                              float next_offset, float next_eps, void* next_out, int ld_next,
+                              int n, int width, void* stream) {
   using namespace ayk;
   if (n == 0) return AYK_OK;
   if (n < 0 || width < 1 || x == nullptr || weight == nullptr || dst == nullptr ||
-      ld_x < width || ld_dst < width || (copy != nullptr && ld_copy < width) || !(eps > 0.f)) {
+      ld_x < width || ld_dst < width || (copy != nullptr && ld_copy < width) || !(eps > 0.f) ||
+      (next_out != nullptr && (next_weight == nullptr || ld_next < width ||
+                               !(next_eps > 0.f)))) {
     return AYK_BAD_ARGUMENT;
   }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  if (copy != nullptr && copy_type == 1) {
+  const bool typed = copy != nullptr || next_out != nullptr;
+  if (typed && copy_type == 1) {
     return launch_kernel(norm_add_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0,
                          (cudaStream_t)stream, 1, x, ld_x, weight, offset, eps, factor, dst,
-                         ld_dst, (__nv_bfloat16*)copy, ld_copy, width);
+                         ld_dst, (__nv_bfloat16*)copy, ld_copy, width, next_weight, next_offset,
+                         next_eps, (__nv_bfloat16*)next_out, ld_next);
   }
-  if (copy != nullptr && copy_type != 0) return AYK_BAD_ARGUMENT;
+  if (typed && copy_type != 0) return AYK_BAD_ARGUMENT;
   return launch_kernel(norm_add_kernel<float>, dim3(n), dim3(threads), 0, (cudaStream_t)stream,
                        1, x, ld_x, weight, offset, eps, factor, dst, ld_dst, (float*)copy,
-                       ld_copy, width);
+                       ld_copy, width, next_weight, next_offset, next_eps, (float*)next_out,
+                       ld_next);
+}
+
+AYK_API int ayk_norm_add(const float* x, int ld_x, const float* weight, float offset, float eps,
+                         float factor, float* dst, int ld_dst, void* copy, int ld_copy,
+                         int copy_type, int n, int width, void* stream) {
+  return ayk_norm_add_next(x, ld_x, weight, offset, eps, factor, dst, ld_dst, copy, ld_copy,
+                           copy_type, nullptr, 0.f, 1.f, nullptr, 0, n, width, stream);
 }

@@ -1817,10 +1817,13 @@ def pooled_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
 
 def norm_add(x: torch.Tensor, weight: torch.Tensor, eps: float, dst: torch.Tensor, *,
              factor: float = 1.0, weight_offset: float = 0.0, copy: torch.Tensor | None = None,
-             rows: int) -> None:
+             rows: int, next_weight: torch.Tensor | None = None, next_eps: float = 1e-6,
+             next_offset: float = 0.0, next_out: torch.Tensor | None = None) -> None:
     """``dst += factor * x * rsqrt(mean(x^2) + eps) * (weight_offset + weight)`` over float32
     rows; with ``copy`` (float32 or bfloat16 ``[N, width]``) the new ``dst`` is also written
-    there, rounded once."""
+    there, rounded once; with ``next_out`` (of ``copy``'s type when both are given) and
+    ``next_weight`` the new ``dst`` also leaves normalised for the sublayer that follows:
+    ``next_out = dst * rsqrt(mean(dst^2) + next_eps) * (next_offset + next_weight)``."""
     op = "norm_add"
     if _left_out and op in _left_out:
         return
@@ -1835,11 +1838,24 @@ def norm_add(x: torch.Tensor, weight: torch.Tensor, eps: float, dst: torch.Tenso
         _need(op, "copy", copy, ndim=2)
         if copy.dtype not in _TYPE or copy.shape[1] != width or rows > copy.shape[0]:
             raise BackendError(f"{op}: the copy does not match dst")
-    status = library("rms_norm").ayk_norm_add(
+    typed = copy
+    if next_out is not None:
+        _need(op, "next_out", next_out, ndim=2)
+        _need(op, "next_weight", next_weight, torch.float32, 1)
+        if next_out.dtype not in _TYPE or next_out.shape[1] != width or \
+                rows > next_out.shape[0] or next_weight.shape[0] != width or \
+                (copy is not None and copy.dtype != next_out.dtype):
+            raise BackendError(f"{op}: the next norm's output does not match dst")
+        typed = next_out
+    status = library("rms_norm").ayk_norm_add_next(
         _ptr(x), c_int(x.stride(0)), _ptr(weight), c_float(weight_offset), c_float(eps),
         c_float(factor), _ptr(dst), c_int(dst.stride(0)), _ptr(copy),
         c_int(0 if copy is None else copy.stride(0)),
-        c_int(0 if copy is None else _TYPE[copy.dtype]), c_int(rows), c_int(width), _stream())
+        c_int(0 if typed is None else _TYPE[typed.dtype]),
+        _ptr(next_weight if next_out is not None else None), c_float(next_offset),
+        c_float(next_eps), _ptr(next_out),
+        c_int(0 if next_out is None else next_out.stride(0)), c_int(rows), c_int(width),
+        _stream())
     check(status, op)
 
 

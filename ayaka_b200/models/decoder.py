@@ -92,8 +92,16 @@ class DecoderModel(Part):
             # every layer can run from the C++ host code: one call walks the whole order
             native.run_layers(runs, native.step_args(step, residual.device), residual)
         else:
+            step.extra.pop("block.normed_by", None)
             for index, run in enumerate(spec.order):
+                # a block that can apply the next layer's first norm on its way out is told
+                # which one that is (and says so in ``step.extra["block.normed_by"]``)
+                following = spec.order[index + 1].layer if index + 1 < len(spec.order) else None
+                step.extra["block.next_norm"] = None if following is None else getattr(
+                    self.blocks[following], "mixer_norm", None)
                 self.blocks[run.layer].forward(residual, step, caches[index])  # type: ignore
+            step.extra.pop("block.next_norm", None)
+            step.extra.pop("block.normed_by", None)
         if num_want == 0 or want_rows is None:
             return None
         chosen = step.workspace.buffer("model.head_in", spec.hidden_size, self.ctx.dtype,

@@ -146,6 +146,12 @@ class ParallelBlock(Block):
         self.feed_forward.forward(hidden, residual, step)  # type: ignore[attr-defined]
 
 
+def _can_follow(norm: object) -> bool:
+    """Whether ``norm`` is a root-mean-square norm that ``ops.norm_add`` can apply on its way
+    out (``weight``, ``offset``, ``eps`` and ``width``)."""
+    return all(hasattr(norm, name) for name in ("weight", "offset", "eps", "width"))
+
+
 def _plain_norm(norm: Part | None) -> bool:
     """Whether ``norm`` declares itself a LayerNorm that a fused kernel can apply from its
     (weight, bias, eps); see ``parts/norm.py``."""
@@ -229,7 +235,14 @@ class SandwichNormBlock(Block):
     The stream is fp32. A sublayer reads its norm's output in the compute type and writes a
     fp32 branch (``forward_into`` where the part has it, else a zeroed branch it adds into);
     the norm behind it adds ``f * norm(branch)`` to the stream in one launch, and for a side
-    part that launch also leaves the new stream rounded once to the compute type."""
+    part that launch also leaves the new stream rounded once to the compute type.
+
+    The norm in front of a sublayer is applied by the launch that last updated the stream (the
+    norm behind the sublayer before it, or the side part's), which holds the new row in
+    registers: the mixer's by the layer before (the model names the next layer's norm in
+    ``step.extra["block.next_norm"]`` and this block marks ``step.extra["block.normed_by"]``
+    when it has applied it), the feed-forward's by this layer's own first half. Only a
+    model's first layer launches a norm of its own."""
 
     def __init__(self, spec: LayerSpec, ctx: BuildContext, position: Part | None) -> None:
         super().__init__(ctx)
@@ -268,23 +281,37 @@ class SandwichNormBlock(Block):
         copy = work.buffer("block.stream", self.width, self.ctx.dtype) \
             if rounded and self.side is not None else None
         last_is_mixer = self.feed_forward_norm is None
-        self.mixer_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
+        # the norm of the layer that follows, if the model named one this block can apply
+        following = step.extra.pop("block.next_norm", None)
+        if not (_can_follow(following) and following.width == self.width):
+            following = None
+        if step.extra.pop("block.normed_by", None) is not self.mixer_norm:
+            self.mixer_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
         if hasattr(self.mixer, "forward_into"):
             self.mixer.forward_into(hidden, branch, step, cache)  # type: ignore[attr-defined]
         else:
             branch[:n].zero_()
             self.mixer.forward(hidden, branch, step, cache)  # type: ignore[attr-defined]
+        # which norm the launch that updates the stream applies on its way out, into `hidden`
+        fused_second = not last_is_mixer and _can_follow(self.feed_forward_norm)
+        after_mixer = self.feed_forward_norm if fused_second else (
+            following if last_is_mixer and self.side is None else None)
         self.mixer_post_norm.add_normed(branch, residual, factor=self.factor,  # type: ignore
-                                        count=n, copy=copy if last_is_mixer else None)
+                                        count=n, copy=copy if last_is_mixer else None,
+                                        then=after_mixer, then_out=hidden)
         if self.feed_forward_norm is not None:
-            self.feed_forward_norm.forward(residual, hidden, count=n)  # type: ignore
+            if not fused_second:
+                self.feed_forward_norm.forward(residual, hidden, count=n)  # type: ignore
             if hasattr(self.feed_forward, "forward_into"):
                 self.feed_forward.forward_into(hidden, branch, step)  # type: ignore
             else:
                 branch[:n].zero_()
                 self.feed_forward.forward(hidden, branch, step)  # type: ignore[attr-defined]
             self.feed_forward_post_norm.add_normed(  # type: ignore[union-attr]
-                branch, residual, factor=self.factor, count=n, copy=copy)
+                branch, residual, factor=self.factor, count=n, copy=copy,
+                then=following if self.side is None else None, then_out=hidden)
         if self.side is not None:
             self.side.forward(copy if rounded else residual, residual, step,  # type: ignore
-                              factor=self.factor)
+                              factor=self.factor, then=following, then_out=hidden)
+        if following is not None:
+            step.extra["block.normed_by"] = following

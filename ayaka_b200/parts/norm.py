@@ -64,9 +64,17 @@ class RMSNorm(Part):
                      count=count)
 
     def add_normed(self, x: torch.Tensor, residual: torch.Tensor, *, factor: float, count: int,
-                   copy: torch.Tensor | None = None) -> None:
+                   copy: torch.Tensor | None = None, then: RMSNorm | None = None,
+                   then_out: torch.Tensor | None = None) -> None:
         """``residual += factor * norm(x)`` over ``count`` fp32 rows (a norm on a sublayer's
         *output*); with ``copy`` the new rows of the stream are also written there in its
-        type, for the sublayer that reads them next."""
-        ops.norm_add(x, self.weight, self.eps, residual, factor=factor,
-                     weight_offset=self.offset, copy=copy, rows=count)
+        type, for the sublayer that reads them next; with ``then`` (the norm in front of the
+        next sublayer) and ``then_out`` that norm's output leaves the same launch."""
+        if then is None or then_out is None:
+            ops.norm_add(x, self.weight, self.eps, residual, factor=factor,
+                         weight_offset=self.offset, copy=copy, rows=count)
+        else:
+            ops.norm_add(x, self.weight, self.eps, residual, factor=factor,
+                         weight_offset=self.offset, copy=copy, rows=count,
+                         next_weight=then.weight, next_eps=then.eps, next_offset=then.offset,
+                         next_out=then_out)

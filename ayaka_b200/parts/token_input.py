@@ -40,9 +40,11 @@ class TokenGatedInput(Part):
         self.norm_weight = self.add_param("norm.weight", (self.width,), "vector")
 
     def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext, *,
-                factor: float = 1.0, copy: torch.Tensor | None = None) -> None:
+                factor: float = 1.0, copy: torch.Tensor | None = None,
+                then: Part | None = None, then_out: torch.Tensor | None = None) -> None:
         """``hidden``: the stream in the compute type; ``residual``: the fp32 stream, updated
-        in place (and ``copy`` with it)."""
+        in place (and ``copy`` with it); ``then`` (an ``rms_norm`` part) with ``then_out``:
+        the norm in front of the next sublayer, applied to the new stream in the same launch."""
         n, work = step.num_rows, step.workspace
         raw = work.buffer("token_input.gate", self.dim, torch.float32)
         gated = work.buffer("token_input.gated", self.dim, self.ctx.dtype)
@@ -51,5 +53,10 @@ class TokenGatedInput(Part):
         ops.gated_unit(raw, gated, activation=self.activation, rows=n, table=self.table,
                        index=step.tokens)
         ops.linear(gated, self.proj_weight, None, branch, rows=n)
-        ops.norm_add(branch, self.norm_weight, self.eps, residual, factor=factor, copy=copy,
-                     rows=n)
+        if then is None or then_out is None:
+            ops.norm_add(branch, self.norm_weight, self.eps, residual, factor=factor, copy=copy,
+                         rows=n)
+        else:
+            ops.norm_add(branch, self.norm_weight, self.eps, residual, factor=factor, copy=copy,
+                         rows=n, next_weight=then.weight, next_eps=then.eps,  # type: ignore
+                         next_offset=then.offset, next_out=then_out)  # type: ignore

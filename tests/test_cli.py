@@ -27,12 +27,12 @@ def test_random_writes_a_model_folder(tmp_path, capsys):
 def test_info_reports_architectures_parts_and_sources(capsys):
     assert cli.main(["info", "--output", "json"]) == cli.EXIT_OK
     report = json.loads(capsys.readouterr().out)
-    assert report["architectures"] == ["GPT2LMHeadModel", "Gagotar", "Mapuvik", "Semadra"]
+    assert report["architectures"] == ["GPT2LMHeadModel", "Gagotar", "Mapuvik", "Rizitar", "Semadra"]
     assert "attention" in report["parts"]["mixer"] and "dense" in report["parts"]["feed_forward"]
     assert "layer_norm" in report["parts"]["norm"] and "learned" in report["parts"]["position"]
     assert {"gemm_tc", "attention_decode", "norm", "sampling"} <= set(report["cuda_sources"])
     assert cli.main(["info"]) == cli.EXIT_OK
-    assert "architectures: GPT2LMHeadModel, Gagotar, Mapuvik, Semadra" in capsys.readouterr().out
+    assert "architectures: GPT2LMHeadModel, Gagotar, Mapuvik, Rizitar, Semadra" in capsys.readouterr().out
 
 
 def test_replay_takes_the_replay_programs_options(tmp_path, capsys):

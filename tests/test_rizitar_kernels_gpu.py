@@ -292,3 +292,30 @@ def test_portions_on_the_flash_kernel(heads, kv_heads, dim, window, pool, rot, p
     got = out.double().cpu()
     assert torch.isfinite(got).all()
     assert float((got - want).abs().max()) <= 3e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [50, 1024, 5000])
+def test_the_norm_behind_a_sublayer_applies_the_next_one_too(width, out_dtype):
+    """``norm_add`` with the following norm: the stream, its rounding and the next sublayer's
+    input from one launch (rows kept in registers, and the wide rows that are not)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(width)
+    rows = 9
+    x = (torch.randn(rows, width, generator=g) * 3).to(DEVICE)
+    dst = torch.randn(rows + 2, width, generator=g).to(DEVICE)
+    w = (1 + 0.3 * torch.randn(width, generator=g)).to(DEVICE)
+    w2 = (1 + 0.3 * torch.randn(width, generator=g)).to(DEVICE)
+    before = dst.clone()
+    copy = torch.full((rows, width), float("nan"), dtype=out_dtype, device=DEVICE)
+    nxt = torch.full((rows, width), float("nan"), dtype=out_dtype, device=DEVICE)
+    ops.norm_add(x, w, 1e-5, dst, factor=0.7, weight_offset=0.25, copy=copy, rows=rows,
+                 next_weight=w2, next_eps=1e-3, next_offset=0.5, next_out=nxt)
+    want = before[:rows].double().cpu().numpy() + 0.7 * plain.rms(
+        x.double().cpu().numpy(), 0.25 + w.double().cpu().numpy(), 1e-5)
+    want_next = plain.rms(want, 0.5 + w2.double().cpu().numpy(), 1e-3)
+    tol = 1e-5 if out_dtype == torch.float32 else 8e-3
+    assert np.allclose(dst[:rows].double().cpu().numpy(), want, rtol=1e-5, atol=1e-5)
+    assert torch.equal(dst[rows:], before[rows:])
+    assert np.allclose(copy.double().cpu().numpy(), want, rtol=tol, atol=tol)
+    assert np.allclose(nxt.double().cpu().numpy(), want_next, rtol=tol, atol=tol)
