@@ -220,9 +220,12 @@ def _class_work(config: dict, rows: int, keys_per_row: float, decode: bool,
         return work
     if config["architecture"] == "Rizitar":
         side = (config.get("token_side") or {}).get("dim", 0)
+        # (only the first layer launches the norm in front of its mixer: every other norm in
+        # front of a sublayer leaves the launch that last updated the stream, `norm_add`,
+        # which then writes one more row in the compute type)
+        add("rms_norm", 0.0, rows * width * 6)
         for layer in config["layers"]:
             m, mlp = layer["mixer"], layer["mlp"]
-            add("rms_norm", 0.0, rows * width * 6)
             if layer["type"] == "attention":
                 H, G, dim = m["heads"], m.get("kv_heads", m["heads"]), m["dim"]
                 window = (m.get("mask") or {}).get("size", 0)
@@ -253,9 +256,8 @@ def _class_work(config: dict, rows: int, keys_per_row: float, decode: bool,
                     rows * 6 * H * N * 4 + (2 * H * N * N * 4) * (rows if decode else PROMPTS))
                 add("rms_norm", 0.0, rows * H * N * 10)
                 product(width, H * N, 4)
-            add("norm_add", 0.0, rows * width * 14)
+            add("norm_add", 0.0, rows * width * 16)
             if mlp is not None:
-                add("rms_norm", 0.0, rows * width * 6)
                 if mlp["kind"] == "dense":
                     product(mlp["ff"], width, 4)
                     add("unary_rows", 0.0, rows * mlp["ff"] * 6)
@@ -267,12 +269,12 @@ def _class_work(config: dict, rows: int, keys_per_row: float, decode: bool,
                     add("moe_experts", 2.0 * rows * top * 2 * f * width,
                         min(E, rows * top) * 2 * f * width * 2 + rows * top * (width * 6 + f * 4))
                     add("moe_join", 0.0, rows * width * (4 * top + 4))
-                add("norm_add", 0.0, rows * width * 14)
+                add("norm_add", 0.0, rows * width * 16)
             if side:
                 product(side, width, 4)
                 add("gated_unit", 0.0, rows * side * 8)
                 product(width, side, 4)
-                add("norm_add", 0.0, rows * width * 14)
+                add("norm_add", 0.0, rows * width * 16)
         add("rms_norm", 0.0, wanted * width * 6)
         product(config["vocab"], width, 4, wanted)
         return work
