@@ -21,10 +21,10 @@
 // square (eps inside the root) and multiplied by one weight of `dim` entries that all heads
 // share; the first `rot_dims` entries of each head are rotated by the row's position (entry i
 // pairs with entry i + rot_dims / 2; cosine and sine times `rot_gain`); queries go to `q` in
-// the compute type, keys into the row's cache slot. With `raw_values` the value of a token is
-// its key as projected, before norm and rotation.
-// blocks (one launch per layer, after prepare): every row whose position ends a block writes
-// that block's means.
+// the compute type, keys into the row's cache slot. Where value pages are given, a token's
+// value is its key as projected, before norm and rotation.
+// blocks (one launch per layer, after prepare): the means of every block whose last position
+// is among the step's rows.
 // attention: one CTA per (row, head) on the CUDA cores, any sizes, both types; steps of
 // single rows cut a row's visible entries into shares (further down). The visible entries
 // are numbered blocks first, then the window's keys, and walked in that order in tiles that
@@ -87,21 +87,36 @@ pooled_prepare_kernel(const float* __restrict__ proj, int ld_proj, int k_off,
   }
 }
 
-// grid (rows, G). The row whose position is the last of a block writes the block's means.
+// grid (candidates, G). A request whose rows of this step run from position p0 to p1 ends the
+// blocks p0 / P .. (p1 + 1) / P - 1; the blocks that all requests end are numbered through, and
+// CTA x takes the x-th of them (none: it leaves). The grid is an upper bound that depends on
+// the step's numbers of rows and requests alone, so that a captured graph's launch holds for
+// every step of its shape. A block's rows are summed in their order, four loads in flight.
 template <typename T>
 __global__ void __launch_bounds__(128)
 pooled_blocks_kernel(const int* __restrict__ positions, const int* __restrict__ request_of_row,
+                     const int* __restrict__ row_start, int requests,
                      const int* __restrict__ block_table, int ld_table,
                      const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                      T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int pool,
                      int pool_slots, int G, int dim, int vdim) {
   pdl_launch_dependents();
-  const int row = blockIdx.x, g = blockIdx.y;
-  const int b = request_of_row[row];
-  const int p = positions[row];
+  const int g = blockIdx.y;
+  int left = blockIdx.x, b = 0, block = -1;
+  for (; b < requests; ++b) {
+    const int r0 = row_start[b], count = row_start[b + 1] - r0;
+    if (count <= 0 || request_of_row[r0] < 0) continue;  // (a request of padding)
+    const int p0 = positions[r0];
+    const int ends = (p0 + count) / pool - p0 / pool;
+    if (left < ends) {
+      block = p0 / pool + left;
+      break;
+    }
+    left -= ends;
+  }
   pdl_wait_for(k_pages, v_pages);
-  if (b < 0 || (p + 1) % pool != 0) return;
-  const int first = p + 1 - pool;
+  if (block < 0) return;
+  const int first = block * pool;
   const int* table = block_table + (size_t)b * ld_table;
   const size_t to_page = table[first / page_size];
   const size_t to = (to_page * G + g) * pool_slots + (first % page_size) / pool;
@@ -109,13 +124,22 @@ pooled_blocks_kernel(const int* __restrict__ positions, const int* __restrict__ 
   for (int d = threadIdx.x; d < dim + vdim; d += blockDim.x) {
     const bool key = d < dim;
     const int c = key ? d : d - dim, width = key ? dim : vdim;
-    const T* pages = key ? k_pages : v_pages;
-    float sum = 0.f;
-    for (int t = 0; t < pool; ++t) {
-      const int at = first + t;
+    const T* pages = (key ? k_pages : v_pages) + c;
+    auto row_of = [&](int at) {
       const size_t page = table[at / page_size];
-      sum += ldf(pages + ((page * G + g) * page_size + at % page_size) * width + c);
+      return ldf(pages + ((page * G + g) * page_size + at % page_size) * width);
+    };
+    float sum = 0.f;
+    int t = 0;
+    for (; t + 4 <= pool; t += 4) {
+      const float v0 = row_of(first + t), v1 = row_of(first + t + 1);
+      const float v2 = row_of(first + t + 2), v3 = row_of(first + t + 3);
+      sum += v0;
+      sum += v1;
+      sum += v2;
+      sum += v3;
     }
+    for (; t < pool; ++t) sum += row_of(first + t);
     stf((key ? k_pool : v_pool) + to * width + c, sum * share);
   }
 }
@@ -464,14 +488,16 @@ int pooled_prepare(const float* proj, int ld_proj, int k_off, const float* q_wei
 }
 
 template <typename T>
-int pooled_blocks(const int* positions, const int* request_of_row, const int* block_table,
-                  int ld_table, const void* k_pages, const void* v_pages, void* k_pool,
-                  void* v_pool, int page_size, int pool, int pool_slots, int rows, int G, int dim,
-                  int vdim, cudaStream_t s) {
-  return launch_kernel(pooled_blocks_kernel<T>, dim3(rows, G), dim3(128), 0, s, 1, positions,
-                       request_of_row, block_table, ld_table, (const T*)k_pages,
-                       (const T*)v_pages, (T*)k_pool, (T*)v_pool, page_size, pool, pool_slots, G,
-                       dim, vdim);
+int pooled_blocks(const int* positions, const int* request_of_row, const int* row_start,
+                  int requests, const int* block_table, int ld_table, const void* k_pages,
+                  const void* v_pages, void* k_pool, void* v_pool, int page_size, int pool,
+                  int pool_slots, int rows, int G, int dim, int vdim, cudaStream_t s) {
+  // blocks a step of `rows` rows in `requests` requests can end, at most
+  const int most = min(rows, rows / pool + requests);
+  return launch_kernel(pooled_blocks_kernel<T>, dim3(most, G), dim3(128), 0, s, 1, positions,
+                       request_of_row, row_start, requests, block_table, ld_table,
+                       (const T*)k_pages, (const T*)v_pages, (T*)k_pool, (T*)v_pool, page_size,
+                       pool, pool_slots, G, dim, vdim);
 }
 
 template <typename T>
@@ -542,13 +568,15 @@ AYK_API int ayk_pooled_prepare(const float* proj, int ld_proj, int k_off, const 
 
 // The means of the blocks that end in this step. pool_slots = ceil(page_size / pool).
 AYK_API int ayk_pooled_blocks(const int* positions, const int* request_of_row,
-                              const int* block_table, int ld_table, const void* k_pages,
-                              const void* v_pages, void* k_pool, void* v_pool, int page_size,
-                              int pool, int pool_slots, int rows, int kv_heads, int dim, int vdim,
-                              int type, void* stream) {
+                              const int* row_start, int requests, const int* block_table,
+                              int ld_table, const void* k_pages, const void* v_pages,
+                              void* k_pool, void* v_pool, int page_size, int pool,
+                              int pool_slots, int rows, int kv_heads, int dim, int vdim, int type,
+                              void* stream) {
   using namespace ayk;
-  if (rows == 0) return AYK_OK;
-  if (rows < 0 || kv_heads < 1 || dim < 1 || vdim < 1 || page_size < 1 || pool < 1 ||
+  if (rows == 0 || requests == 0) return AYK_OK;
+  if (rows < 0 || requests < 0 || row_start == nullptr || kv_heads < 1 || dim < 1 || vdim < 1 ||
+      page_size < 1 || pool < 1 ||
       pool_slots != (page_size + pool - 1) / pool || positions == nullptr ||
       request_of_row == nullptr || block_table == nullptr || k_pages == nullptr ||
       v_pages == nullptr || k_pool == nullptr || v_pool == nullptr || kv_heads > 65535) {
@@ -556,14 +584,15 @@ AYK_API int ayk_pooled_blocks(const int* positions, const int* request_of_row,
   }
   cudaStream_t s = (cudaStream_t)stream;
   if (type == 0) {
-    return pooled_blocks<float>(positions, request_of_row, block_table, ld_table, k_pages,
-                                v_pages, k_pool, v_pool, page_size, pool, pool_slots, rows,
-                                kv_heads, dim, vdim, s);
+    return pooled_blocks<float>(positions, request_of_row, row_start, requests, block_table,
+                                ld_table, k_pages, v_pages, k_pool, v_pool, page_size, pool,
+                                pool_slots, rows, kv_heads, dim, vdim, s);
   }
   if (type == 1) {
-    return pooled_blocks<__nv_bfloat16>(positions, request_of_row, block_table, ld_table,
-                                        k_pages, v_pages, k_pool, v_pool, page_size, pool,
-                                        pool_slots, rows, kv_heads, dim, vdim, s);
+    return pooled_blocks<__nv_bfloat16>(positions, request_of_row, row_start, requests,
+                                        block_table, ld_table, k_pages, v_pages, k_pool, v_pool,
+                                        page_size, pool, pool_slots, rows, kv_heads, dim, vdim,
+                                        s);
   }
   return AYK_BAD_ARGUMENT;
 }

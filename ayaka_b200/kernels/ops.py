@@ -1715,10 +1715,12 @@ def pool_slots(page_size: int, pool: int) -> int:
 
 def pooled_blocks(k_pages: torch.Tensor, v_pages: torch.Tensor, k_pool: torch.Tensor,
                   v_pool: torch.Tensor, block_table: torch.Tensor, request_of_row: torch.Tensor,
-                  positions: torch.Tensor, *, pool: int, rows: int) -> None:
-    """For every row of the step whose position is the last of a block of ``pool`` positions:
-    the mean of the block's cached keys into ``k_pool`` and of its cached values into
-    ``v_pool`` (``[pages, kv_heads, pool_slots, dim]``), in the page of the block's first
+                  positions: torch.Tensor, row_start: torch.Tensor, *, pool: int, rows: int,
+                  requests: int) -> None:
+    """For every block of ``pool`` positions whose last position is among the step's rows
+    (request ``b`` brings the rows ``row_start[b] .. row_start[b + 1]`` at consecutive
+    positions): the mean of the block's cached keys into ``k_pool`` and of its cached values
+    into ``v_pool`` (``[pages, kv_heads, pool_slots, dim]``), in the page of the block's first
     position, at slot ``(first % page_size) // pool``."""
     op = "pooled_blocks"
     if _left_out and op in _left_out:
@@ -1730,6 +1732,7 @@ def pooled_blocks(k_pages: torch.Tensor, v_pages: torch.Tensor, k_pool: torch.Te
     _need(op, "block_table", block_table, torch.int32, 2)
     _need(op, "request_of_row", request_of_row, torch.int32, 1)
     _need(op, "positions", positions, torch.int32, 1)
+    _need(op, "row_start", row_start, torch.int32, 1)
     pages, kv_heads, page_size, dim = k_pages.shape
     vdim = v_pages.shape[3]
     slots = pool_slots(page_size, pool) if pool > 0 else 0
@@ -1737,10 +1740,12 @@ def pooled_blocks(k_pages: torch.Tensor, v_pages: torch.Tensor, k_pool: torch.Te
             tuple(k_pool.shape) != (pages, kv_heads, slots, dim) or \
             tuple(v_pool.shape) != (pages, kv_heads, slots, vdim) or \
             not all(t.is_contiguous() for t in (k_pages, v_pages, k_pool, v_pool)) or \
-            rows > positions.shape[0] or rows > request_of_row.shape[0]:
+            rows > positions.shape[0] or rows > request_of_row.shape[0] or \
+            row_start.shape[0] < requests + 1 or block_table.shape[0] < requests:
         raise BackendError(f"{op}: shapes do not fit")
     status = library("pooled_attention").ayk_pooled_blocks(
-        _ptr(positions), _ptr(request_of_row), _ptr(block_table), c_int(block_table.stride(0)),
+        _ptr(positions), _ptr(request_of_row), _ptr(row_start), c_int(requests),
+        _ptr(block_table), c_int(block_table.stride(0)),
         _ptr(k_pages), _ptr(v_pages), _ptr(k_pool), _ptr(v_pool), c_int(page_size), c_int(pool),
         c_int(slots), c_int(rows), c_int(kv_heads), c_int(dim), c_int(vdim),
         c_int(_TYPE[k_pages.dtype]), _stream())

@@ -139,7 +139,8 @@ class PooledWindowAttention(Mixer):
         if self.pool and cache.writes:
             ops.pooled_blocks(cache.k_pages, cache.v_pages, cache.k_pool, cache.v_pool,
                               group.block_table, step.request_of_row, step.positions,
-                              pool=self.pool, rows=n)
+                              step.row_start, pool=self.pool, rows=n,
+                              requests=step.num_requests)
         # Prompt portions in bfloat16, where the sizes are the tensor-core kernel's: the
         # engine's flash kernel, told of the pooled rows and the sink. Single rows (a decode
         # step, or the decoding requests that lead a mixed step) go to the kernel of shares,

@@ -209,7 +209,8 @@ def _attention_case(dtype, heads, kv_heads, dim, window, pool, rot, page, length
             if slots:
                 ops.pooled_blocks(k_pages, v_pages, k_pool, v_pool, table_d[b:b + 1],
                                   torch.zeros(size, dtype=torch.int32, device=DEVICE), positions,
-                                  pool=pool, rows=size)
+                                  torch.tensor([0, size], dtype=torch.int32, device=DEVICE),
+                                  pool=pool, rows=size, requests=1)
             at += size
     return dict(ops=ops, projections=projections, answers=answers, table=table_d,
                 k_pages=k_pages, v_pages=v_pages, k_pool=k_pool, v_pool=v_pool, sink=sink,
