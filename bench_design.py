@@ -107,8 +107,8 @@ def rizitar_config(width: int, heads: int, ff: int, repeats: int, vocab: int) ->
     head = width // heads
     attention = {"heads": heads, "kv_heads": heads // 4, "dim": head, "vdim": head,
                  "scale": head ** -0.5, "mask": {"size": RIZITAR_WINDOW, "pool": RIZITAR_POOL},
-                 "rot": {"base": 10000.0, "dims": head,
-                         "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0,
+                 "rot": {"base": 500000.0, "dims": head,
+                         "scaling": {"factor": 4.0, "original": 8192, "fast": 16.0,
                                      "slow": 1.0}}}
     memory = {"heads": width // 64, "dim": 64, "decay_rank": 64}
     moe = {"kind": "moe", "expert": {"ff": ff // 4},

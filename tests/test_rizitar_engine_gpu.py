@@ -344,3 +344,21 @@ def test_experts_far_more_than_chosen_and_all_chosen(tmp_path):
     core = support.build_core(folder, "float32", num_blocks=12)
     got = support.replay(core, support.schedule_mixed(sequences, pool_tokens=128))
     support.assert_logits_close(got, expected, "float32", "rizitar-experts")
+
+
+def test_bfloat16_with_sizes_that_are_multiples_of_nothing(tmp_path):
+    """Width 50, heads of 10 and 7, inner widths 35 and 9, a vocabulary of 101, a token input
+    of 3: the bfloat16 path where no row is a whole number of 16-byte pieces."""
+    config = model(101, 50, 1e-5, [
+        layer(attention(3, 1, 10, 13, 3, rot=6, base=50.0), dense(35)),
+        layer(delta(2, 7, 5), moe(5, 2, 9)),
+        layer(attention(2, 2, 14, 6, 4, rot=14, base=200.0, scaling=(4.0, 16, 8.0, 1.0))),
+    ], embed_scale=3.0, side=3)
+    folder, state = support.make_model(tmp_path / "m", config, 13, LOUD, "bfloat16")
+    sequences = _sequences(config, (70, 2, 33), seed=13)
+    expected = plain_logits(state, config, sequences)
+    for steps in (support.schedule_whole(sequences),
+                  support.schedule_mixed(sequences, pool_tokens=128)):
+        core = support.build_core(folder, "bfloat16", num_blocks=12)
+        got = support.replay(core, steps)
+        assert_mostly_close(got, expected, "rizitar-odd/bfloat16")
